@@ -29,6 +29,9 @@ class KVRequest:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    # the values are the keys (attention over one latent record per position): one plane is stored,
+    # and a layer's view hands it out as both
+    values_are_keys: bool = False
 
 
 @dataclass(frozen=True)
@@ -51,9 +54,11 @@ class CacheGroup:
         self.num_pages = num_pages
         self.dtype = dtype
         self.max_pages_per_seq = max_pages_per_seq
-        # [layer][k|v][page][kv_head][pos][dim]
+        # [layer][k|v][page][kv_head][pos][dim] (one plane where the values are the keys)
+        self.values_are_keys = bool(req.values_are_keys)
         self.storage = torch.zeros(
-            (len(cache_ids), 2, num_pages, req.num_kv_heads, PAGE_TOKENS, req.head_dim), dtype=dtype, device=device
+            (len(cache_ids), 1 if self.values_are_keys else 2, num_pages, req.num_kv_heads, PAGE_TOKENS, req.head_dim),
+            dtype=dtype, device=device
         )
         # one row per slot plus the padding row, whose entries stay 0 (the scratch page)
         self.table = torch.zeros((max_slots + 1, max_pages_per_seq), dtype=torch.int32, device=device)
@@ -69,7 +74,7 @@ class CacheView:
         self.group = group
         self.layer = layer
         self.k = group.storage[layer, 0]
-        self.v = group.storage[layer, 1]
+        self.v = group.storage[layer, 0 if group.values_are_keys else 1]
 
 
 class KVCache:

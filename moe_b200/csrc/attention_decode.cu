@@ -402,7 +402,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
             a += f * __ldcg(base + (size_t)sp * REC + d);
         }
         write_head_column((T*)fa.out, GateOut{fa.gate, fa.gate_ld, fa.dv}, t, nh, h, HD, d,
-                          a / attn_denominator(mm, ll, av.sink));
+                          a / attn_denominator(mm, ll, av.sink, attn_sink_value(av, h)));
     }
 }
 
@@ -547,7 +547,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 template <typename T>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                          const int* __restrict__ seq_of_token, int nh, int hd, int nsplit,
-                                         const GateOut go, int sink) {
+                                         const GateOut go, const AttnVariant av) {
     pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const int rec = hd + 2;
@@ -570,7 +570,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* _
             const float ms = base[(size_t)s * rec + hd];
             if (ms != -INFINITY) a += expf(ms - mm) * base[(size_t)s * rec + d];
         }
-        write_head_column(out, go, t, nh, h, hd, d, a / attn_denominator(mm, ll, sink));
+        write_head_column(out, go, t, nh, h, hd, d, a / attn_denominator(mm, ll, av.sink, attn_sink_value(av, h)));
     }
 }
 
@@ -593,7 +593,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
            const int* seq_of_token, const int* pos, const int* slots, const int* tables, int table_stride, int ring,
            int page_size, int num_pages, int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
            int* status, cudaStream_t stream, const FusedArgs* fused = nullptr, const GateOut go = GateOut{nullptr, 0, 0},
-           const AttnVariant av = AttnVariant{0, 0.f, 0}) {
+           const AttnVariant av = AttnVariant{0, 0.f, 0, nullptr}) {
     const int group = nh / nkv;
     dim3 grid(nsplit, nkv, num_tokens);
     const int row_bytes = hd * (int)sizeof(T);
@@ -644,7 +644,7 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
 #undef FAST_G
     if (fused || rc) return rc;
     return launch_pdl(attn_decode_merge_kernel<T>, dim3(num_tokens, nh), 128, 0, stream, (const float*)partial, (T*)out,
-                      seq_of_token, nh, hd, nsplit, go, av.sink);
+                      seq_of_token, nh, hd, nsplit, go, av);
 }
 
 }  // namespace
@@ -688,11 +688,11 @@ MOE_API int moe_attention_decode(const void* q, const void* k_cache, const void*
                                  const int* tables, int table_stride, int ring, int page_size, int num_pages,
                                  int num_tokens, int nh, int nkv, int hd, int window, float scale, int nsplit,
                                  const float* gate, int gate_ld, int dv, int* status, int chunk, float softcap,
-                                 int sink, cudaStream_t stream) {
+                                 int sink, const float* sink_vals, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (dv < 0 || dv > hd || (gate && dv == 0)) return (int)cudaErrorInvalidValue;
     const GateOut go{gate, gate_ld, dv};
-    const AttnVariant av{chunk, softcap, sink};
+    const AttnVariant av{chunk, softcap, sink, sink_vals};
     if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh <= 0 || nh > 65535 || nh % nkv != 0 || nsplit < 1 ||
         nsplit > 65535 || nkv > 65535 || num_tokens > 65535 || !q || !k_cache || !v_cache || !out || !partial)
         return (int)cudaErrorInvalidValue;

@@ -112,7 +112,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const 
             }
         }
     }
-    const float inv = 1.0f / attn_denominator(m, l, av.sink);
+    const float inv = 1.0f / attn_denominator(m, l, av.sink, attn_sink_value(av, h));
 #pragma unroll
     for (int i = 0; i < MAX_HD / 32; i++) {
         const int d = lane + 32 * i;
@@ -127,8 +127,8 @@ MOE_API int moe_attention_generic(const void* q, const void* k_new, const void* 
                                   const int* seq_start, const int* cu_seqlens, const int* slots, const int* tables,
                                   int table_stride, int ring, int page_size, int num_pages, int num_tokens, int nh,
                                   int nkv, int hd, int window, float scale, int use_local, int* status,
-                                  int chunk, float softcap, int sink, cudaStream_t stream) {
-    const AttnVariant av{chunk, softcap, sink};
+                                  int chunk, float softcap, int sink, const float* sink_vals, cudaStream_t stream) {
+    const AttnVariant av{chunk, softcap, sink, sink_vals};
     if (num_tokens <= 0) return 0;
     if (hd % 16 != 0 || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535)
         return (int)cudaErrorInvalidValue;

@@ -523,8 +523,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         // the row's sum: the two halves, in a fixed order
         if (ok) {
-            // (a sink: one more term of score 0, which carries no value; both halves hold the same m)
-            x_sum[half][r] = (av.sink && half == 0 && m != -INFINITY) ? l + ex2_approx(-m) : l;
+            // (a sink: one more term, of score 0 or the head's own number, which carries no value; both
+            // halves hold the same m, which is in units of log 2)
+            x_sum[half][r] = (av.sink && half == 0 && m != -INFINITY)
+                                 ? l + ex2_approx(attn_sink_value(av, head) * 1.4426950408889634f - m) : l;
             __syncwarp();
             if (lane == 0) mbar_arrive(x_bar(qd));
             ok = mbar_wait(x_bar(qd), n_tiles & 1, &s_abort, status, 0x4c);
@@ -655,14 +657,15 @@ int run(const void* q, const void* k, const void* v, CacheArgs& c, void* out, co
 // does not take: the caller then uses moe_attention_prefill_bf16.
 MOE_API int moe_attention_prefill_tc(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens,
                                      int num_seqs, int num_tokens, int nh, int nkv, int hd, int window, float scale,
-                                     int* status, int chunk, float softcap, int sink, cudaStream_t stream) {
+                                     int* status, int chunk, float softcap, int sink,
+        const float* sink_vals, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
     if (hd != 64 && hd != 128) return -1;
     if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) != 0) return -1;
     CacheArgs c{};
     return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status,
-               AttnVariant{chunk, softcap, sink}, stream);
+               AttnVariant{chunk, softcap, sink, sink_vals}, stream);
 }
 
 // The same for sequences that go on from the cache: sequence i held seq_start[i] tokens before the
@@ -675,7 +678,8 @@ MOE_API int moe_attention_cached_tc(const void* q, const void* k, const void* v,
                                     const void* v_cache, void* out, const int* cu_seqlens, const int* seq_start,
                                     const int* slots, const int* tables, int table_stride, int ring, int page_size,
                                     int num_pages, int num_seqs, int num_tokens, int nh, int nkv, int hd, int window,
-                                    float scale, int* status, int chunk, float softcap, int sink, cudaStream_t stream) {
+                                    float scale, int* status, int chunk, float softcap, int sink,
+        const float* sink_vals, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || nh > 65535 || num_pages <= 0) return (int)cudaErrorInvalidValue;
     if (!seq_start || !slots || !tables || !k_cache || !v_cache) return (int)cudaErrorInvalidValue;
@@ -690,5 +694,5 @@ MOE_API int moe_attention_cached_tc(const void* q, const void* k, const void* v,
         !make_cache_map(&c.tmV, v_cache, (long long)num_pages * nkv * 64, hd))
         return -1;
     return run(q, k, v, c, out, cu_seqlens, num_seqs, num_tokens, nh, nkv, hd, window, scale, status,
-               AttnVariant{chunk, softcap, sink}, stream);
+               AttnVariant{chunk, softcap, sink, sink_vals}, stream);
 }

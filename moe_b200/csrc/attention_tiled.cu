@@ -207,7 +207,7 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
     for (int r = 0; r < 4; r++) {
         const int row = ty * 4 + r;
         if (row >= rows) continue;
-        const float inv = l[r] > 0.f ? 1.0f / attn_denominator(m[r], l[r], var.sink) : 0.f;
+        const float inv = l[r] > 0.f ? 1.0f / attn_denominator(m[r], l[r], var.sink, attn_sink_value(var, h)) : 0.f;
         T* dst = out + ((size_t)(tok0 + r0 + row) * nh + h) * hd;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -235,9 +235,9 @@ MOE_API int moe_attention_tiled(const void* q, const void* k_new, const void* v_
                                 const int* slots, const int* tables, int table_stride, int ring, int page_size,
                                 int num_pages, int num_seqs, int num_tokens, int nh, int nkv, int hd, int window,
                                 float scale, int use_local, int* status, int chunk, float softcap, int sink,
-                                cudaStream_t stream) {
+                                const float* sink_vals, cudaStream_t stream) {
     if (num_tokens <= 0 || num_seqs <= 0) return 0;
-    const AttnVariant av{chunk, softcap, sink};
+    const AttnVariant av{chunk, softcap, sink, sink_vals};
     if (hd % 16 != 0 || hd > 256 || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
     if (page_size != BK || (ring % BK) != 0) return -1;
     const size_t align = dt == DT_F32 ? 16 : 8;          // rows are read four elements at a time

@@ -95,13 +95,18 @@ __device__ __forceinline__ float glu_mul(int act, float param, float g, float u)
 //   chunk > 0   position p sees the keys of its own chunk only: lo = (p / chunk) * chunk (chunks are
 //               counted from position 0 of the sequence); else window > 0: lo = max(0, p + 1 - window)
 //   softcap > 0 the scaled score s becomes softcap * tanh(s / softcap)
-//   sink        the softmax has one more term of score 0 that carries no value: the denominator
-//               is 1 + sum_j exp(s_j)
+//   sink        the softmax has one more term that carries no value: the denominator is
+//               exp(b_h) + sum_j exp(s_j), with b_h = sink_vals[h] for query head h (a learned number
+//               per head, neither scaled nor capped) or 0 where sink_vals is null
 struct AttnVariant {
     int chunk;
     float softcap;
     int sink;
+    const float* sink_vals;
 };
+__device__ __forceinline__ float attn_sink_value(const AttnVariant& av, int h) {
+    return (av.sink && av.sink_vals) ? av.sink_vals[h] : 0.f;
+}
 __device__ __forceinline__ int attn_lo(int p, int window, int chunk) {
     return chunk > 0 ? (p / chunk) * chunk : (window > 0 ? max(0, p + 1 - window) : 0);
 }
@@ -110,8 +115,9 @@ __device__ __forceinline__ float attn_score(float dot, float scale, float softca
     return softcap > 0.f ? softcap * tanhf(s / softcap) : s;
 }
 // the denominator of a softmax whose running maximum is m and running sum (relative to m) is l
-__device__ __forceinline__ float attn_denominator(float m, float l, int sink) {
-    return sink ? l + expf(-m) : l;
+// (sv: the sink's own score)
+__device__ __forceinline__ float attn_denominator(float m, float l, int sink, float sv = 0.f) {
+    return sink ? l + expf(sv - m) : l;
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }

@@ -231,7 +231,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
                                             int num_experts, int rows, int top_k, int norm_topk, float scale,
                                             int* __restrict__ idx_out, float* __restrict__ w_out,
                                             float* __restrict__ gate_out, float* wk = nullptr,
-                                            const float* __restrict__ bias = nullptr) {
+                                            const float* __restrict__ bias = nullptr, int groups = 0, int keep = 0) {
     // wk: top_k floats of shared memory for the picked weights before scaling (else they are
     // staged in w_out itself, which costs round trips to global memory)
     if (!wk) wk = w_out;
@@ -254,6 +254,42 @@ __device__ __forceinline__ void route_token(const float* __restrict__ lg, float*
     z = warp_sum(z);
     for (int e = lane; e < num_experts; e += 32) sc[e] = sc[e] / z;
     __syncwarp();
+    if (groups > 1 && keep > 0 && keep < groups) {
+        // Experts form `groups` equal groups of neighbours; a group's score is its best expert's, and
+        // only experts of the `keep` best groups (the lower group first among equals) may be picked.
+        // A kept group is marked by the sign bit of its scores (scores are never negative, and the
+        // flip is exact); afterwards the marked scores get their sign back and the others are taken
+        // out of the pick.
+        const int gsz = num_experts / groups;
+        for (int j = 0; j < keep; j++) {
+            float best = -1.f;
+            int bg = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float* s = sc + (size_t)g * gsz;
+                if (__float_as_uint(s[0]) >> 31) continue;          // kept already
+                float v = s[0];
+                for (int i = 1; i < gsz; i++) v = fmaxf(v, s[i]);
+                if (v > best) best = v, bg = g;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+                if (ob > best || (ob == best && og < bg)) best = ob, bg = og;
+            }
+            if (bg < 0 || bg >= groups) break;                       // only with NaN scores
+            for (int i = lane; i < gsz; i += 32) {
+                float* s = sc + (size_t)bg * gsz + i;
+                *s = __uint_as_float(__float_as_uint(*s) | 0x80000000u);
+            }
+            __syncwarp();
+        }
+        for (int e = lane; e < groups * gsz; e += 32) {
+            const unsigned u = __float_as_uint(sc[e]);
+            sc[e] = (u >> 31) ? __uint_as_float(u & 0x7fffffffu) : -2.f;
+        }
+        __syncwarp();
+    }
     float wsum = 0.f;
     for (int j = 0; j < top_k; j++) {
         float best = -1.f;
@@ -301,7 +337,7 @@ __global__ void __launch_bounds__(128)
 router_topk_kernel(float* __restrict__ logits, const float* __restrict__ part, int slices,
                    const int* __restrict__ seq_of_token, int num_tokens, int num_experts, int rows, int top_k,
                    int norm_topk, float scale, int* __restrict__ topk_idx, float* __restrict__ topk_w,
-                   float* __restrict__ shared_gate, const float* __restrict__ bias) {
+                   float* __restrict__ shared_gate, const float* __restrict__ bias, int groups, int keep) {
     extern __shared__ float sc_all[];   // per warp: rows logits, num_experts scores, top_k weights
     pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -323,7 +359,7 @@ router_topk_kernel(float* __restrict__ logits, const float* __restrict__ part, i
     __syncwarp();
     route_token(lg, lg + rows, lane, seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
                 topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr,
-                lg + rows + num_experts, bias);
+                lg + rows + num_experts, bias, groups, keep);
 }
 
 // Inverting the (token, expert) table, by one block.  pairs = tokens * top_k entries of topk_idx
@@ -383,7 +419,8 @@ route_dispatch_kernel(const float* __restrict__ logits, const int* __restrict__ 
                       int num_experts, int rows, int top_k, int norm_topk, float scale, int* __restrict__ topk_idx,
                       float* __restrict__ topk_w, float* __restrict__ shared_gate, int* __restrict__ offsets,
                       int* __restrict__ sorted_token, int* __restrict__ pos_of_pair, const uint4* __restrict__ x,
-                      uint4* __restrict__ xs, int row_units, int* status, const float* __restrict__ bias) {
+                      uint4* __restrict__ xs, int row_units, int* status, const float* __restrict__ bias,
+                      int groups, int keep) {
     extern __shared__ float dyn[];   // 32 warps x num_experts floats, then counts[E], cursor[E]
     pdl_sync();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -391,7 +428,7 @@ route_dispatch_kernel(const float* __restrict__ logits, const int* __restrict__ 
         route_token(logits + (size_t)t * rows, dyn + (size_t)warp * num_experts, lane,
                     seq_of_token && seq_of_token[t] < 0, num_experts, rows, top_k, norm_topk, scale,
                     topk_idx + (size_t)t * top_k, topk_w + (size_t)t * top_k, shared_gate ? shared_gate + t : nullptr,
-                    nullptr, bias);
+                    nullptr, bias, groups, keep);
     __syncthreads();   // the picks were written by this block: visible to it after the barrier
     int* counts = reinterpret_cast<int*>(dyn + (size_t)32 * num_experts);
     const int pairs = num_tokens * top_k;
@@ -878,9 +915,11 @@ MOE_API int moe_router_logits(const float* h, const void* wr, const void* wsg, i
 MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt, const int* seq_of_token,
                        int num_tokens, int hidden, int num_experts, int top_k, int norm_topk, float scale,
                        float* logits, int* topk_idx, float* topk_w, float* shared_gate, float* scratch,
-                       long long scratch_floats, const float* bias, cudaStream_t stream) {
+                       long long scratch_floats, const float* bias, int groups, int keep, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits) return (int)cudaErrorInvalidValue;
+    if (groups > 1 && (num_experts % groups || keep < 1 || keep > groups || top_k > keep * (num_experts / groups)))
+        return (int)cudaErrorInvalidValue;
     if (wsg && !shared_gate) return (int)cudaErrorInvalidValue;
     int slices = 0;
     const int rc = router_logits_impl(h, wr, wsg, w_dt, num_tokens, hidden, num_experts, logits, scratch,
@@ -895,15 +934,17 @@ MOE_API int moe_router(const float* h, const void* wr, const void* wsg, int w_dt
     }
     return launch_pdl(router_topk_kernel, (num_tokens + 3) / 4, 128, smem, stream, logits,
                       (const float*)(slices ? scratch : nullptr), slices, seq_of_token, num_tokens, num_experts, rows,
-                      top_k, norm_topk, scale, topk_idx, topk_w, shared_gate, bias);
+                      top_k, norm_topk, scale, topk_idx, topk_w, shared_gate, bias, groups, keep);
 }
 
 // Picks, weights and shared gate from logits that are already there ([T, rows] float32).
 MOE_API int moe_router_topk(float* logits, const int* seq_of_token, int num_tokens, int num_experts, int has_gate_row,
                             int top_k, int norm_topk, float scale, int* topk_idx, float* topk_w, float* shared_gate,
-                            const float* bias, cudaStream_t stream) {
+                            const float* bias, int groups, int keep, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (top_k <= 0 || top_k > num_experts || num_experts > 2048 || !logits || (has_gate_row && !shared_gate))
+        return (int)cudaErrorInvalidValue;
+    if (groups > 1 && (num_experts % groups || keep < 1 || keep > groups || top_k > keep * (num_experts / groups)))
         return (int)cudaErrorInvalidValue;
     const int rows = num_experts + (has_gate_row ? 1 : 0);
     const size_t smem = (size_t)4 * (rows + num_experts + top_k) * sizeof(float);
@@ -914,7 +955,7 @@ MOE_API int moe_router_topk(float* logits, const int* seq_of_token, int num_toke
     }
     return launch_pdl(router_topk_kernel, (num_tokens + 3) / 4, 128, smem, stream, logits, (const float*)nullptr, 0,
                       seq_of_token, num_tokens, num_experts, rows, top_k, norm_topk, scale, topk_idx, topk_w, shared_gate,
-                      bias);
+                      bias, groups, keep);
 }
 
 // A float32 row as three bfloat16 terms, x = p0 + p1 + p2 exactly (8 + 8 + 8 bits of mantissa):
@@ -964,14 +1005,18 @@ MOE_API int moe_align(const int* topk_idx, int num_tokens, int top_k, int num_ex
 MOE_API int moe_route_dispatch(const float* logits, const int* seq_of_token, int num_tokens, int num_experts,
                                int has_gate_row, int top_k, int norm_topk, float scale, int* topk_idx, float* topk_w,
                                float* shared_gate, int* offsets, int* sorted_token, int* pos_of_pair, const void* x,
-                               void* xs, int row_bytes, int* status, const float* bias, cudaStream_t stream) {
+                               void* xs, int row_bytes, int* status, const float* bias, int groups, int keep,
+                               cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (num_tokens > 64 || num_experts > 256 || top_k <= 0 || top_k > num_experts || row_bytes % 16)
+        return (int)cudaErrorInvalidValue;
+    if (groups > 1 && (num_experts % groups || keep < 1 || keep > groups || top_k > keep * (num_experts / groups)))
         return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)32 * num_experts * sizeof(float) + (size_t)2 * num_experts * sizeof(int);
     return launch_pdl(route_dispatch_kernel, 1, 1024, smem, stream, logits, seq_of_token, num_tokens, num_experts,
                       num_experts + (has_gate_row ? 1 : 0), top_k, norm_topk, scale, topk_idx, topk_w, shared_gate,
-                      offsets, sorted_token, pos_of_pair, (const uint4*)x, (uint4*)xs, row_bytes / 16, status, bias);
+                      offsets, sorted_token, pos_of_pair, (const uint4*)x, (uint4*)xs, row_bytes / 16, status, bias, groups,
+                      keep);
 }
 
 MOE_API int moe_swiglu(const float* gu, void* act, int out_dt, long long rows, int inter, int f, float f_param,

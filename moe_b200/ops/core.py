@@ -36,21 +36,25 @@ def lib():
             "moe_dyt": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
             "moe_heads_prepare": [P, I, P, P, P, P, F, P, I, F, I, I, I, I, I, I, P, P, P, LL, LL, I, P, P, P, P, P, I, I, I, I, P, P],
             "moe_gate_pack": [P, P, I, I, I, I, I, P, I, P],
+            "moe_latent_prepare": [P, I, P, P, P, F, I, I, I, I, I, P, P, I, P, P, P, P, P, I, I, I, I, P, P],
+            "moe_heads_transpose": [P, I, LL, LL, I, I, I, I, P, I, P],
+            "moe_diff_combine": [P, P, I, I, I, I, I, F, F, F, P, I, P],
+            "moe_add_row": [P, P, P, LL, I, P],
             "moe_rmsnorm": [P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_rmsnorm_combine": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, F, I, P, P],
             "moe_add_inplace": [P, P, LL, P],
             "moe_gemm_generic": [P, I, I, P, I, P, I, LL, P, I, I, P, P, I, I, I, I, P, P],
             "moe_rope_split": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, P, P],
             "moe_kv_commit": [P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
-            "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, F, I, P],
-            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, LL, P, P],
+            "moe_attention_generic": [P, P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, F, I, P, P],
+            "moe_router": [P, P, P, I, P, I, I, I, I, I, F, P, P, P, P, P, LL, P, I, I, P],
             "moe_router_logits": [P, P, P, I, I, I, I, P, P, LL, P],
-            "moe_router_topk": [P, P, I, I, I, I, I, F, P, P, P, P, P],
+            "moe_router_topk": [P, P, I, I, I, I, I, F, P, P, P, P, I, I, P],
             "moe_split3": [P, P, LL, I, P],
-            "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P, P],
+            "moe_route_dispatch": [P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P, I, P, P, I, I, P],
             "moe_rope_commit": [P, P, P, I, I, I, I, I, P, P, P, I, P, P, P, I, I, I, I, P, P],
-            "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, I, F, I, P],
-            "moe_attention_tiled": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, I, F, I, P],
+            "moe_attention_decode": [P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, I, F, I, P, P],
+            "moe_attention_tiled": [P, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, I, F, I, P, P],
             "moe_conv_heads_prepare": [P, I, P, I, P, LL, P, P, P, P, F, I, P, I, I, I, I, I, I, I, P, P, P, LL, LL, I, P, P,
                                        P, P, I, I, I, I, P, P],
             "moe_conv_state_update": [P, I, P, LL, I, I, P, P, I, P],
@@ -343,6 +347,70 @@ def gate_pack(ctx, out, *, nh, dv, width, gate=None):
     _ok(lib().moe_gate_pack(_p(ctx), _p(gate), ld, T, nh, dv, width, _p(out), _dt(out), _stream()), "gate_pack")
 
 
+def latent_prepare(proj, batch, *, nh, d, r, width, weight, eps, q_t, k_new, commit=None, status=None):
+    """From a step's 32-bit projection rows [q heads (nh x d) | latent (r)]: the latent divided by its
+    root mean square, times ``weight``, into ``k_new`` [T, width] (zero-filled beyond r) and, with
+    ``commit`` (a cache view), appended to that cache layer; the queries head by head into ``q_t``
+    [nh, T, d]."""
+    _chk(proj, "proj", torch.float32, 2), _chk(weight, "latent norm weight", torch.float32, 1)
+    T = proj.shape[0]
+    _chk(q_t, "q_t"), _chk(k_new, "k_new")
+    if (proj.shape[1] < nh * d + r or weight.numel() != r or q_t.numel() != nh * T * d or k_new.numel() != T * width
+            or q_t.dtype != k_new.dtype or width < r):
+        raise KernelError("latent_prepare: shapes or dtypes")
+    kc = vc = se = sl = tb = None
+    ts = ring = ps = npg = 0
+    if commit is not None:
+        g = commit.group
+        if k_new.dtype != g.dtype or g.num_kv_heads != 1 or g.head_dim != width:
+            raise KernelError("latent_prepare: the cache layer differs from the latent in dtype or shape")
+        kc, vc, se, sl, tb = commit.k, commit.v, batch.seq_end, batch.slots, g.table
+        ts, ring, ps, npg = g.table.stride(0), g.ring, g.page_size, g.num_pages
+    _ok(lib().moe_latent_prepare(_p(proj), proj.stride(0), _p(batch.pos), _p(batch.seq_of_token), _p(weight), float(eps),
+                                 T, nh, d, r, width, _p(q_t), _p(k_new), _dt(k_new), _p(kc), _p(vc), _p(se), _p(sl),
+                                 _p(tb), ts, ring, ps, npg, _p(status), _stream()), "latent_prepare")
+
+
+def heads_transpose(src, dst, *, n):
+    """dst[b, a, :n] = src[a, b, :n], zero beyond n; src: [A, B, >= n] with unit stride along the last
+    axis (any pitch of the other two), dst: dense [B, A, wd >= n]; float32 or bfloat16 on either side."""
+    if (src.dim() != 3 or dst.dim() != 3 or not dst.is_contiguous() or src.stride(2) != 1 or src.shape[2] < n
+            or dst.shape[2] < n or (dst.shape[0], dst.shape[1]) != (src.shape[1], src.shape[0])):
+        raise KernelError("heads_transpose: shapes")
+    A, B = src.shape[0], src.shape[1]
+    _ok(lib().moe_heads_transpose(_p(src), _dt(src), src.stride(0), src.stride(1), A, B, int(n), dst.shape[2], _p(dst),
+                                  _dt(dst), _stream()), "heads_transpose")
+
+
+def diff_combine(ctx, out, *, nh, dv, width, lam, eps, mult, gate=None):
+    """Joins the two maps of differential attention: with a1 = ctx[t, h, :dv] and a2 = ctx[t, nh + h, :dv]
+    (ctx: [T, 2 nh, width]), o = a1 - lam a2, o / sqrt(mean(o^2) + eps) * mult * sigmoid(gate[t, h]) into
+    out[t, h * dv : (h + 1) * dv]; ``gate``: a float32 column slice [T, nh] of a projection, or None."""
+    _chk(ctx, "ctx"), _chk(out, "out", dims=2)
+    T = out.shape[0]
+    if ctx.numel() < T * 2 * nh * width or out.shape[1] != nh * dv or out.dtype != ctx.dtype or width < dv:
+        raise KernelError("diff_combine: shapes or dtypes")
+    ld = 0
+    if gate is not None:
+        if gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or tuple(gate.shape) != (T, nh):
+            raise KernelError("diff_combine: gate shape, dtype or layout")
+        ld = gate.stride(0)
+    _ok(lib().moe_diff_combine(_p(ctx), _p(gate), ld, T, nh, dv, width, float(lam), float(eps), float(mult), _p(out),
+                               _dt(out), _stream()), "diff_combine")
+
+
+def add_row(x, row, delta=None):
+    """x[t, :] += delta[t, :] + row[:] in 32-bit (``delta`` may be None)."""
+    _chk(x, "x", torch.float32, 2), _chk(row, "row", torch.float32, 1)
+    if row.numel() != x.shape[1]:
+        raise KernelError("add_row: the row's width")
+    if delta is not None:
+        _chk(delta, "delta", torch.float32, 2)
+        if delta.shape != x.shape:
+            raise KernelError("add_row: the delta's shape")
+    _ok(lib().moe_add_row(_p(x), _p(delta), _p(row), x.shape[0], x.shape[1], _stream()), "add_row")
+
+
 def conv_heads_prepare(proj, batch, *, nh, nkv, d, dv, width, q, k, v, taps_w=None, state=None, eps=0.0,
                        unit_norm=False, freq=None, rot=0, commit=None, status=None):
     """From a step's 32-bit projection rows [q heads | k heads | v heads]: a causal convolution over
@@ -604,8 +672,13 @@ def kv_commit(k_new, v_new, view, batch, status):
 
 
 def _variant(chunk, softcap, sink):
-    """(chunk, softcap, sink) as the kernels take them: see AttnVariant in csrc/common.cuh."""
-    return int(chunk or 0), float(softcap or 0.0), 1 if sink else 0
+    """(chunk, softcap, sink, the sink's values per head) as the kernels take them: see AttnVariant in
+    csrc/common.cuh.  ``sink``: False, True (a term of score 0) or a float32 tensor with one number
+    per query head (the term's own score)."""
+    if isinstance(sink, torch.Tensor):
+        _chk(sink, "sink", torch.float32, 1)
+        return int(chunk or 0), float(softcap or 0.0), 1, sink.data_ptr()
+    return int(chunk or 0), float(softcap or 0.0), 1 if sink else 0, None
 
 
 def attention_generic(q, k_new, v_new, view, batch, out, *, nh, window, scale, use_local, status, chunk=0,
@@ -653,8 +726,10 @@ def _router_bias(bias, E):
 
 
 def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_gate_w=None, shared_gate=None,
-           seq_of_token=None, bias=None):
-    """``bias``: float32 [E], added to the logits before the softmax and the pick."""
+           seq_of_token=None, bias=None, groups=0, keep=0):
+    """``bias``: float32 [E], added to the logits before the softmax and the pick.  ``groups``, ``keep``:
+    the experts form ``groups`` equal groups of neighbours, and only experts of the ``keep`` groups
+    whose best score is largest may be picked (0: no groups)."""
     _chk(h32, "h", torch.float32, 2), _chk(w_router, "router weight", dims=2)
     T, H = h32.shape
     E = w_router.shape[0]
@@ -673,7 +748,7 @@ def router(h32, w_router, top_k, norm_topk, scale, topk_idx, topk_w, *, shared_g
     scratch = torch.empty((need,), dtype=torch.float32, device=h32.device) if need else None
     _ok(lib().moe_router(_p(h32), _p(w_router), _p(shared_gate_w), _dt(w_router), _p(seq_of_token), T, H, E, top_k,
                          1 if norm_topk else 0, float(scale), _p(logits), _p(topk_idx), _p(topk_w), _p(shared_gate),
-                         _p(scratch), need, _p(_router_bias(bias, E)), _stream()), "router")
+                         _p(scratch), need, _p(_router_bias(bias, E)), int(groups), int(keep), _stream()), "router")
 
 
 def split3(x32: torch.Tensor) -> torch.Tensor:
@@ -686,7 +761,7 @@ def split3(x32: torch.Tensor) -> torch.Tensor:
 
 
 def router_topk(logits, top_k, norm_topk, scale, topk_idx, topk_w, *, num_experts, shared_gate=None, seq_of_token=None,
-                bias=None):
+                bias=None, groups=0, keep=0):
     """Picks and weights from logits [T, E (+ 1 row for the shared gate)] that are already there."""
     _chk(logits, "logits", torch.float32, 2)
     T = logits.shape[0]
@@ -695,7 +770,7 @@ def router_topk(logits, top_k, norm_topk, scale, topk_idx, topk_w, *, num_expert
         raise KernelError("router_topk: logits must have one column per expert (and one for the shared gate)")
     _ok(lib().moe_router_topk(_p(logits), _p(seq_of_token), T, num_experts, 1 if gate_row else 0, top_k,
                               1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(shared_gate),
-                              _p(_router_bias(bias, num_experts)), _stream()),
+                              _p(_router_bias(bias, num_experts)), int(groups), int(keep), _stream()),
         "router_topk")
 
 
@@ -942,7 +1017,7 @@ def norm_route(x, delta, norm_w, eps, w_router, top_k, norm_topk, scale, *, bf16
 
 
 def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None, seq_of_token=None, gather=None,
-                   status=None, bias=None):
+                   status=None, bias=None, groups=0, keep=0):
     """Few tokens (<= 64) and <= 256 experts: router logits, then pick + table inversion + gather in
     ONE more launch.  Returns (topk_idx, topk_w, shared_gate, offsets, sorted_token, pos_of_pair,
     gathered) where ``gathered[p] = gather[sorted_token[p]]`` (or None)."""
@@ -972,5 +1047,5 @@ def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None
     _ok(lib().moe_route_dispatch(_p(logits), _p(seq_of_token), T, E, 1 if shared_gate_w is not None else 0, top_k,
                                  1 if norm_topk else 0, float(scale), _p(topk_idx), _p(topk_w), _p(sg), _p(offsets),
                                  _p(sorted_token), _p(pos_of_pair), _p(gather), _p(xs), row_bytes, _p(status),
-                                 _p(_router_bias(bias, E)), _stream()), "route_dispatch")
+                                 _p(_router_bias(bias, E)), int(groups), int(keep), _stream()), "route_dispatch")
     return topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs

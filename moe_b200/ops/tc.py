@@ -35,9 +35,9 @@ def lib():
 
         L.moe_attention_prefill_bf16.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P]
         L.moe_attention_prefill_bf16.restype = c_int
-        L.moe_attention_prefill_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P, I, c_float, I, P]
+        L.moe_attention_prefill_tc.argtypes = [P, P, P, P, P, I, I, I, I, I, I, c_float, P, I, c_float, I, P, P]
         L.moe_attention_prefill_tc.restype = c_int
-        L.moe_attention_cached_tc.argtypes = [P] * 10 + [I] * 10 + [c_float, P, I, c_float, I, P]
+        L.moe_attention_cached_tc.argtypes = [P] * 10 + [I] * 10 + [c_float, P, I, c_float, I, P, P]
         L.moe_attention_cached_tc.restype = c_int
         L.moe_tc_set_pdl.argtypes = [c_int]
         L.moe_tc_set_pdl.restype = None
@@ -205,7 +205,7 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch, 
     if q.dtype != torch.bfloat16 or hd not in (16, 32, 64, 128):
         return False
     variant = core._variant(chunk, softcap, sink)
-    plain = variant == (0, 0.0, 0)
+    plain = variant == (0, 0.0, 0, None)
     if not plain and not (hd in (64, 128) and status is not None and _ATTN_TC):
         return False
     if hd in (64, 128) and status is not None and _ATTN_TC:

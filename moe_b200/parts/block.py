@@ -4,7 +4,8 @@ Pre-norm with two residual sums (src/model.rs:669-684):
     n = norm1(x); x += mixer(n); n = norm2(x); x += ffn(n)
 The residual stream ``x`` is float32.  The last sum of a block is left pending
 and folded into the next norm (of the next block, or the final one), which
-reads and writes the stream once instead of twice.
+reads and writes the stream once instead of twice.  The feed-forward (with its
+norm) may be absent: x += mixer(norm1(x)) is then the whole layer.
 
 "Sandwich": a norm before AND after each sublayer, and the feed-forward optional:
     x += post1(mixer(norm1(x)));  x += post2(ffn(norm2(x)))
@@ -30,13 +31,15 @@ class PreNormBlock:
 
     def __init__(self, layer: LayerSpec):
         self.layer = layer
+        if (layer.ffn is None) != (layer.norm2 is None):
+            raise ValueError("a pre-norm block has a feed-forward with its norm, or neither")
         self.norm1 = make_part("norm", layer.norm1)
         self.mixer = make_part("mixer", layer.mixer)
-        self.norm2 = make_part("norm", layer.norm2)
-        self.ffn = make_part("ffn", layer.ffn)
+        self.norm2 = make_part("norm", layer.norm2) if layer.norm2 is not None else None
+        self.ffn = make_part("ffn", layer.ffn) if layer.ffn is not None else None
 
     def parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.ffn]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
     def forward(self, rt, x, pending, batch, cache_view, state):
         """x: [T, hidden] float32 stream; pending: a delta not yet added (or None).
@@ -44,6 +47,8 @@ class PreNormBlock:
         h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt),
                                want32=getattr(self.mixer, "wants32", False))
         delta = self.mixer.forward(rt, h, batch, cache_view, state)
+        if self.ffn is None:          # a layer without a feed-forward: its mixer's output is what is pending
+            return x, delta
         # a feed-forward may offer to run the norm before it itself (fused with its first
         # kernels); it returns None where it cannot, and nothing has happened then
         prenorm = getattr(self.ffn, "forward_prenorm", None)

@@ -128,6 +128,46 @@ class ConcatLinearJoin(Part):
         return linear(rt, self._both, self.weight)
 
 
+class AddRowJoin(Part):
+    """x <- x + w[row]: one row of a learned table [rows, hidden] is added to every token's stream (a
+    model that runs a stretch of its layers several times adds row t at the start of pass t).  The
+    sum is 32-bit and takes along whatever was still pending."""
+
+    category, kind = "join", "add_row"
+    graph_safe = True
+    default_names = {"weight": "weight"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.params["hidden_size"])
+        self.rows = int(self.params["rows"])
+        self.row = int(self.params["row"])
+        if not 0 <= self.row < self.rows:
+            raise ValueError(f"add_row: row {self.row} of a table of {self.rows}")
+
+    def tensors(self):
+        return {self.names["weight"]: TensorSpec((self.rows, self.hidden), vector=True)}
+
+    def describe(self):
+        return f"adds row {self.row} of a table of {self.rows} vectors"
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.vector = tensors[self.names["weight"]][self.row].to(torch.float32).contiguous()
+
+    def remember(self, rt, x0):
+        pass
+
+    def forward(self, rt, x, pending):
+        from .base import LazyDelta
+
+        if isinstance(pending, LazyDelta):
+            pending = pending.materialize(rt)
+        core.add_row(x, self.vector, delta=pending)
+        return x
+
+
 register_part("join", "concat_linear", ConcatLinearJoin)
+register_part("join", "add_row", AddRowJoin)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("head", "lm_head", LMHead)

@@ -106,6 +106,15 @@ class RoutedExperts(Part):
         self.shared_size = int(p.get("shared_size", 0) or 0)
         self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_size > 0
         self.router_bias = bool(p.get("router_bias", False))     # logits = Wr n + b
+        # {"count": g, "keep": m}: the experts form g equal groups of neighbours, a group's score is its
+        # best expert's, and only experts of the m best groups may be picked
+        grp = p.get("groups") or {}
+        self.groups, self.keep = int(grp.get("count", 0) or 0), int(grp.get("keep", 0) or 0)
+        if self.groups <= 1 or self.keep >= self.groups:
+            self.groups = self.keep = 0                          # every group kept: no limit at all
+        elif self.E % self.groups or self.keep < 1 or self.k > self.keep * (self.E // self.groups):
+            raise ValueError("router groups: the count must divide the experts, and the kept groups must hold top_k experts")
+        self._grp = dict(groups=self.groups, keep=self.keep)
         if not 0 < self.k <= self.E:
             raise ValueError("top_k must lie in 1..num_experts")
         # Set to a list to record every routing decision as (expert ids [T, k], weights [T, k]);
@@ -168,6 +177,7 @@ class RoutedExperts(Part):
     def describe(self):
         return (f"{self.E} experts of {self.size}, top-{self.k}, softmax gate"
                 + (" with bias" if self.router_bias else "")
+                + (f", within the best {self.keep} of {self.groups} groups" if self.groups else "")
                 + (", renormalised" if self.norm_topk else "")
                 + (f", scaled by {self.scale:g}" if self.scale != 1.0 else "")
                 + (f", shared expert {self.shared_size}" + (" (gated)" if self.shared_gate else "")
@@ -249,11 +259,12 @@ class RoutedExperts(Part):
                 if after_logits is not None:
                     after_logits()
                 core.router_topk(logits, self.k, self.norm_topk, self.scale, topk_idx, topk_w, num_experts=self.E,
-                                 shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None), bias=self.b_router)
+                                 shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None), bias=self.b_router,
+                                 **self._grp)
                 return topk_idx, topk_w, sg
         core.router(h.f32, self.w_router, self.k, self.norm_topk, self.scale, topk_idx, topk_w,
                     shared_gate_w=self.w_sgate, shared_gate=sg, seq_of_token=getattr(batch, "seq_of_token", None),
-                    bias=self.b_router)
+                    bias=self.b_router, **self._grp)
         if after_logits is not None:
             after_logits()
         return topk_idx, topk_w, sg
@@ -273,7 +284,8 @@ class RoutedExperts(Part):
         tokens, norm, router and dispatch are one launch.  None if the sizes or the kind of norm do
         not allow it (the block then runs the norm itself and calls ``forward``)."""
         rms = getattr(norm, "rms_params", None)          # the norm says whether it can be run by a neighbour
-        if rms is None or x.shape[0] > self.fused_norm_tokens or self.E > 256 or self.b_router is not None:
+        if (rms is None or x.shape[0] > self.fused_norm_tokens or self.E > 256 or self.b_router is not None
+                or self.groups):
             return None
         norm_w, norm_eps = rms()
         routed = core.norm_route(x, delta, norm_w, norm_eps, self.w_router, self.k, self.norm_topk, self.scale,
@@ -306,7 +318,7 @@ class RoutedExperts(Part):
                 h.f32, self.w_router, self.k, self.norm_topk, self.scale, shared_gate_w=self.w_sgate,
                 seq_of_token=getattr(batch, "seq_of_token", None),
                 gather=h.act if h.act.dtype == torch.bfloat16 and T <= 16 else None, status=rt.status,
-                bias=self.b_router)
+                bias=self.b_router, **self._grp)
             # (more tokens: the gather by that one block would take longer than a launch of its own)
         else:
             def shared_beside():

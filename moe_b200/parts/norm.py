@@ -21,12 +21,14 @@ class RMSNorm(Part):
         super().__init__(spec)
         self.size = int(self.params["size"])
         self.eps = float(self.params["eps"])
+        # a weight stored around zero: the factor is offset + w (the sum is formed once, in 32-bit, when bound)
+        self.offset = float(self.params.get("offset", 0.0) or 0.0)
 
     def tensors(self):
-        return {self.names["weight"]: TensorSpec((self.size,), init="ones", vector=True)}
+        return {self.names["weight"]: TensorSpec((self.size,), init="zeros" if self.offset else "ones", vector=True)}
 
     def describe(self):
-        return f"RMSNorm eps {self.eps:g}"
+        return f"RMSNorm eps {self.eps:g}" + (f", weight {self.offset:g} + w" if self.offset else "")
 
     def rms_params(self):
         """(weight, eps): what a neighbour needs to run this norm inside a kernel of its own (a
@@ -37,6 +39,8 @@ class RMSNorm(Part):
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.weight = tensors[self.names["weight"]].to(torch.float32).contiguous()
+        if self.offset:
+            self.weight = (self.weight + self.offset).contiguous()
 
     def normed32(self, rt, t):
         out = rt.empty(t.shape, torch.float32)

@@ -118,7 +118,7 @@ def test_calls_in_a_row_match_the_ordinary_entry_point_and_a_plain_restatement(d
             q.data_ptr(), view.k.data_ptr(), view.v.data_ptr(), want.data_ptr(), partial.data_ptr(),
             0 if dt == torch.float32 else 1, step.seq_of_token.data_ptr(), step.pos.data_ptr(), step.slots.data_ptr(),
             g.table.data_ptr(), g.table.stride(0), g.ring, g.page_size, g.num_pages, B, nh, nkv, hd, int(window or 0),
-            scale, nsplit, None, 0, 0, st.data_ptr(), 0, 0.0, 0, torch.cuda.current_stream().cuda_stream)
+            scale, nsplit, None, 0, 0, st.data_ptr(), 0, 0.0, 0, None, torch.cuda.current_stream().cuda_stream)
         assert rc == 0
         got = torch.full((B, nh * hd), float("nan"), device=DEV, dtype=dt)
         code = call_noalloc(L, q, view, step, got, dt, B, nh, nkv, hd, window, scale, nsplit, st)
