@@ -165,16 +165,42 @@ def route(scores, top, groups, keep):
     return picked, wts / (wts.sum(-1, keepdim=True) + 1e-20)
 
 
-def moe(w, p, ml, n, picks=None):
-    """Routed experts plus the gated shared one.  ``picks`` [T, top] overrides the choice of experts
-    (the weights still come from this function's scores)."""
+def choice_margin(z, free, mine, groups):
+    """How far the router logits z [E] of one token are from giving ``mine`` instead of ``free``: if
+    the two choices lie in different sets of groups, the gap between the best logits of the groups
+    that were swapped; else the gap between the logits of the experts that were swapped."""
+    E = z.numel()
+    gs = E // max(groups, 1)
+    ga, gb = {e // gs for e in free}, {e // gs for e in mine}
+    if groups > 1 and ga != gb and (ga - gb) and (gb - ga):
+        best = z.reshape(groups, gs).max(-1).values
+        return float(max(best[g] for g in ga - gb) - min(best[g] for g in gb - ga))
+    a, b = set(free), set(mine)
+    if not (a - b) or not (b - a):
+        return 0.0
+    return float(max(z[e] for e in a - b) - min(z[e] for e in b - a))
+
+
+def moe(w, p, ml, n, forced=None, margins=None):
+    """Routed experts plus the gated shared one.  ``forced`` [T, top] replaces the choice of experts
+    (the weights still come from this function's scores); ``margins`` (a list) then receives, for
+    every token whose forced choice differs from the free one, ``choice_margin`` as a fraction of the
+    root mean square of the layer's router logits."""
     r = ml["router"]
     E, top = int(r["experts"]), int(r["top"])
     g = r.get("groups") or {}
-    scores = torch.softmax(n @ w[p + ".router"].T, dim=-1)
+    z = n @ w[p + ".router"].T
+    scores = torch.softmax(z, dim=-1)
     picked, wts = route(scores, top, int(g.get("count", 1)), int(g.get("keep", 1)))
-    if picks is not None:
-        picked = picks.to(torch.int64)
+    if forced is not None:
+        mine = torch.as_tensor(forced, dtype=torch.int64)
+        if margins is not None:
+            scale = float(z.pow(2).mean().sqrt().clamp(min=1e-30))
+            for t in range(n.shape[0]):
+                a, b = sorted(picked[t].tolist()), sorted(mine[t].tolist())
+                if a != b:
+                    margins.append(choice_margin(z[t], a, b, int(g.get("count", 1))) / scale)
+        picked = mine
         wts = scores.gather(1, picked)
         wts = wts / (wts.sum(-1, keepdim=True) + 1e-20)
     out = torch.zeros_like(n)
@@ -201,10 +227,12 @@ def layer_order(cfg):
     return order + [(l, None) for l in range(b, n)]
 
 
-def forward(cfg, w, tokens, layers_out=None, picks=None):
+def forward(cfg, w, tokens, layers_out=None, forced=None, margins=None):
     """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the stream after every
-    layer run; ``picks``: per layer run, the experts to take instead of this function's own choice."""
+    layer run; ``forced`` / ``margins``: the routed layers' choices, one entry per RUN of a layer with
+    routed experts, in the order they run (see ``moe``)."""
     eps = float(cfg["norm"]["eps"])
+    forced = list(forced) if forced is not None else None
     x = w["embed"][torch.tensor(tokens)]
     for run, (l, starts) in enumerate(layer_order(cfg)):
         L, p = cfg["layers"][l], f"l{l}"
@@ -220,7 +248,7 @@ def forward(cfg, w, tokens, layers_out=None, picks=None):
         if L.get("mlp"):
             assert L["mlp"]["kind"] == "moe"
             x = x + moe(w, p + ".mlp", L["mlp"], offset_norm(x, w[p + ".norm2"], eps),
-                        None if picks is None else picks[run])
+                        forced.pop(0) if forced is not None else None, margins)
         if layers_out is not None:
             layers_out.append(x.clone())
     return offset_norm(x, w["final.norm"], eps) @ w["head"].T
