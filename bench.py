@@ -525,6 +525,25 @@ def _median_ms(fn, reps=5, warmup=3):
     return sorted(times)[len(times) // 2]
 
 
+def _graph_ms(fn, calls=10, reps=5):
+    """Device time of one call of ``fn`` whose kernels are shorter than the host's work to launch them:
+    ``calls`` calls captured in a CUDA graph, the median of ``reps`` replays, divided by ``calls``."""
+    import torch
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(calls):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    return _median_ms(g.replay, reps=reps, warmup=2) / calls
+
+
 def supevik_kernels(sh, pk):
     """The new design's own kernels beside the like kernels of the closest model, each alone at 8,192
     tokens (what a call reads and writes exceeds L2), as a fraction of the measured copy bandwidth
@@ -825,6 +844,244 @@ def run_fogapel(args):
     return 0
 
 
+# Zosipel at sizes that resemble a real model's layers, and beside each the library's closest model at
+# equal size: Qwen2 MoE with as many layers as the Zosipel shape has layer RUNS, the same width, heads,
+# experts, expert and shared sizes and vocabulary, every layer routed, heads of twice a map's size (a
+# differential head is two maps), windows of the same size on every layer.
+ZOSIPEL_SHAPES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=64, vdim=128, window=1024, rot=64, softcap=30.0, diff=0.3,
+                  lat_heads=16, lat_dim=128, lat_vdim=128, rank=128, experts=32, top=4, groups=(8, 4), expert_ff=704,
+                  shared_ff=2816, order=("latent_attention", "attention", "latent_attention", "latent_attention", "attention",
+                                         "latent_attention"), loop=(1, 3, 2), vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=64, vdim=128, window=2048, rot=64, softcap=30.0, diff=0.3,
+                  lat_heads=32, lat_dim=128, lat_vdim=128, rank=128, experts=32, top=4, groups=(8, 4), expert_ff=1408,
+                  shared_ff=5632, order=("latent_attention", "attention", "latent_attention", "attention"), loop=(0, 2, 2),
+                  vocab=32768),
+}
+
+
+def zosipel_config(sh):
+    att = {"heads": sh["heads"], "kv_heads": sh["kv_heads"], "dim": sh["dim"], "vdim": sh["vdim"], "scale": sh["dim"] ** -0.5,
+           "softcap": sh["softcap"], "diff": sh["diff"], "mask": {"size": sh["window"]},
+           "rot": {"dims": sh["rot"], "base": 1e6, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    lat = {"heads": sh["lat_heads"], "dim": sh["lat_dim"], "vdim": sh["lat_vdim"], "kv_rank": sh["rank"],
+           "scale": sh["lat_dim"] ** -0.5}
+    moe = {"kind": "moe", "router": {"experts": sh["experts"], "top": sh["top"],
+                                     "groups": {"count": sh["groups"][0], "keep": sh["groups"][1]}},
+           "expert": {"ff": sh["expert_ff"]}, "shared": {"ff": sh["shared_ff"]}}
+    a, b, t = sh["loop"]
+    return {"architecture": "Zosipel", "vocab": sh["vocab"], "width": sh["width"], "norm": {"eps": 1e-5},
+            "loop": {"start": a, "stop": b, "times": t},
+            "layers": [{"type": t_, "mixer": att if t_ == "attention" else lat, "mlp": moe} for t_ in sh["order"]]}
+
+
+def zosipel_qwen_config(sh):
+    a, b, t = sh["loop"]
+    runs = len(sh["order"]) + (b - a) * (t - 1)
+    return dict(architectures=["Qwen2MoeForCausalLM"], model_type="qwen2_moe", num_hidden_layers=runs,
+                hidden_size=sh["width"], num_attention_heads=sh["heads"], num_key_value_heads=sh["kv_heads"],
+                head_dim=2 * sh["dim"], num_experts=sh["experts"], num_experts_per_tok=sh["top"],
+                moe_intermediate_size=sh["expert_ff"], shared_expert_intermediate_size=sh["shared_ff"],
+                norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[], intermediate_size=sh["shared_ff"],
+                vocab_size=sh["vocab"], rope_theta=1e6, rms_norm_eps=1e-5, use_sliding_window=True,
+                sliding_window=sh["window"], max_window_layers=0, tie_word_embeddings=False,
+                max_position_embeddings=8192, qkv_bias=True)
+
+
+def zosipel_kernels(sh, pk):
+    """The new design's own kernels beside the like kernels of the closest model, each alone at 8,192
+    tokens of 4 sequences (what a call reads and writes exceeds L2), as a fraction of the measured copy
+    bandwidth (attention and products: of the measured bf16 peak, counting the products the mechanism
+    needs, not the zero-filled part of a record); then the attention of one token of 64 sequences at a
+    context of 2,048 (the cache read once; ten calls replayed from a CUDA graph, since a call's kernels
+    are shorter than the host's work to launch them)."""
+    import torch
+
+    from moe_b200.cache.kv import KVCache, KVRequest
+    from moe_b200.ops import core, tc
+    from moe_b200.ops.linear import grouped_linear
+    from moe_b200.parts.base import Runtime
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import gpu_util as G
+
+    dev = "cuda:0"
+    bf = torch.bfloat16
+    B, n = 4, 2048
+    T, W = B * n, sh["width"]
+    H, Gk, d, dv, win = sh["heads"], sh["kv_heads"], sh["dim"], sh["vdim"], sh["window"]
+    LH, ld_, lv, rk = sh["lat_heads"], sh["lat_dim"], sh["lat_vdim"], sh["rank"]
+    status = core.new_status(dev)
+    rt = Runtime(dev, bf)
+    r = lambda *s: torch.randn(*s, device=dev)
+    out = {}
+
+    def row(name, ms, nbytes=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if nbytes:
+            e["gb_s"] = round(nbytes / ms / 1e6, 0)
+            e["of_copy_peak"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tflops"] = round(flops / ms / 1e9, 0)
+            e["of_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)
+        out[name] = e
+
+    batch = G.make_batch(dev, list(range(1, B + 1)), [0] * B, [n] * B)
+    freq = torch.rand(sh["rot"] // 2, device=dev)
+    # ---- between projection and attention -------------------------------------------------------------
+    D = max(2 * d, dv)                                   # one record width for maps and values, as the part chooses it
+    nh2, nkv2 = 2 * H, 2 * Gk
+    cols = (nh2 + nkv2) * d + nkv2 * dv + H
+    proj = r(T, cols)
+    q, k, v = (torch.empty((T, m, D), dtype=bf, device=dev) for m in (nh2, nkv2, nkv2))
+    row("heads_prepare (rotation of both maps + split into records)", _median_ms(lambda: core.heads_prepare(
+        proj, batch.pos, batch.seq_of_token, nh=nh2, nkv=nkv2, d=d, dv=dv, width=D, q=q, k=k, v=v, freq=freq, rot=sh["rot"],
+        mscale=1.1, status=status)), T * (cols - H) * 4 + T * (nh2 + 2 * nkv2) * D * 2)
+    wq = (H + 2 * Gk) * 2 * d
+    qkv = r(T, wq)
+    q1, k1, v1 = (torch.empty((T, m, 2 * d), dtype=bf, device=dev) for m in (H, Gk, Gk))
+    row("rope_split (rotation + split)", _median_ms(lambda: core.rope_split(qkv, batch.pos, freq, H, Gk, 2 * d, sh["rot"], q1, k1, v1)),
+        T * wq * (4 + 2))
+    lproj = r(T, LH * ld_ + rk)
+    q_t = torch.empty((LH, T, ld_), dtype=bf, device=dev)
+    k_new = torch.empty((T, 1, rk), dtype=bf, device=dev)
+    wn = r(rk)
+    row("latent_prepare (latent norm + record + queries head by head)", _median_ms(lambda: core.latent_prepare(
+        lproj, batch, nh=LH, d=ld_, r=rk, width=rk, weight=wn, eps=1e-5, q_t=q_t, k_new=k_new, status=status)),
+        T * (LH * ld_ + rk) * (4 + 2))
+    qc = r(LH, T, rk)
+    ql = torch.empty((T, LH, rk), dtype=bf, device=dev)
+    row("heads_transpose (32-bit [heads, tokens] -> 16-bit [tokens, heads])", _median_ms(lambda: core.heads_transpose(qc, ql, n=rk)),
+        T * LH * rk * (4 + 2))
+    # ---- attention of whole prompts: keys a query sees, 4 flops a key and dimension of the mechanism -------
+    seen = sum(min(p + 1, win) for p in range(n)) * B
+    causal = n * (n + 1) // 2 * B
+    qq, kk, vv = (torch.randn(T, m, D, device=dev).to(bf) for m in (nh2, nkv2, nkv2))
+    ctx = torch.empty((T, nh2, D), dtype=bf, device=dev)
+    row("tcgen05 attention, two maps a head (window + capped scores)", _median_ms(lambda: tc.attention_prefill(
+        qq, kk, vv, batch, ctx, nh=nh2, nkv=nkv2, hd=D, window=win, scale=d ** -0.5, status=status, softcap=sh["softcap"])),
+        flops=2.0 * seen * nh2 * (d + dv))
+    qs, ks, vs = (torch.randn(T, m, 2 * d, device=dev).to(bf) for m in (H, Gk, Gk))
+    ctx1 = torch.empty((T, H, 2 * d), dtype=bf, device=dev)
+    row("tcgen05 attention, window", _median_ms(lambda: tc.attention_prefill(
+        qs, ks, vs, batch, ctx1, nh=H, nkv=Gk, hd=2 * d, window=win, scale=d ** -0.5, status=status)), flops=4.0 * seen * H * 2 * d)
+    sinks = r(LH)
+    lq, lk = torch.randn(T, LH, rk, device=dev).to(bf), torch.randn(T, 1, rk, device=dev).to(bf)
+    lctx = torch.empty((T, LH, rk), dtype=bf, device=dev)
+    row("tcgen05 attention over latents (all heads on one record, sink a head)", _median_ms(lambda: tc.attention_prefill(
+        lq, lk, lk, batch, lctx, nh=LH, nkv=1, hd=rk, window=None, scale=ld_ ** -0.5, status=status, sink=sinks)),
+        flops=4.0 * causal * LH * rk)
+    row("tcgen05 attention, causal", _median_ms(lambda: tc.attention_prefill(
+        qs, ks, vs, batch, ctx1, nh=H, nkv=Gk, hd=2 * d, window=None, scale=d ** -0.5, status=status)), flops=4.0 * causal * H * 2 * d)
+    # ---- after attention ---------------------------------------------------------------------------------
+    packed = torch.empty((T, H * dv), dtype=bf, device=dev)
+    row("diff_combine (difference + head norm + gate + pack)", _median_ms(lambda: core.diff_combine(
+        ctx, packed, nh=H, dv=dv, width=D, lam=0.4, eps=1e-5, mult=0.7, gate=proj[:, cols - H:])), T * H * dv * (2 + 2 + 2))
+    row("gate_pack (sigmoid gate on the heads)", _median_ms(lambda: core.gate_pack(ctx1, packed, nh=H, dv=2 * d, width=2 * d,
+                                                                                  gate=proj[:, :H * 2 * d])), T * H * 2 * d * (2 + 4 + 2))
+    # ---- the per-head products of latent attention (a group a head) ----------------------------------------
+    offsets = (torch.arange(0, LH + 1, dtype=torch.int32, device=dev) * T).contiguous()
+    w_qc = (torch.randn(LH, rk, ld_, device=dev) / 16).to(bf)
+    row("queries onto the latent (grouped product, a group a head)",
+        _median_ms(lambda: grouped_linear(rt, q_t.view(LH * T, ld_), w_qc, offsets, LH * T)), T * LH * (ld_ * 2 + rk * 4),
+        flops=2.0 * T * LH * ld_ * rk)
+    I = sh["expert_ff"]
+    xs = torch.randn(T * sh["top"], W, device=dev).to(bf)
+    w_e = (torch.randn(sh["experts"], 2 * I, W, device=dev) / 32).to(bf)
+    eo = (torch.arange(0, sh["experts"] + 1, dtype=torch.int32, device=dev) * (T * sh["top"] // sh["experts"])).contiguous()
+    row("experts' gate|up (grouped product, a group an expert)",
+        _median_ms(lambda: grouped_linear(rt, xs, w_e, eo, T * sh["top"])), flops=2.0 * T * sh["top"] * 2 * I * W)
+    # ---- the router's pick ---------------------------------------------------------------------------------
+    E, top = sh["experts"], sh["top"]
+    logits = r(T, E)
+    idx = torch.empty((T, top), dtype=torch.int32, device=dev)
+    wt = torch.empty((T, top), dtype=torch.float32, device=dev)
+    nb = T * (E * 4 + top * 8)
+    row("router pick within the best groups", _median_ms(lambda: core.router_topk(
+        logits, top, True, 1.0, idx, wt, num_experts=E, groups=sh["groups"][0], keep=sh["groups"][1])), nb)
+    row("router pick", _median_ms(lambda: core.router_topk(logits, top, True, 1.0, idx, wt, num_experts=E)), nb)
+    # ---- one token of 64 sequences at a context of 2,048: the cache read once ---------------------------------
+    S, ctxlen = 64, 2048
+
+    def decode_case(nh, nkv, hd, window, latent, **kw):
+        cache = KVCache({0: KVRequest(nkv, hd, window, values_are_keys=latent)}, {0: None}, max_tokens=S * (ctxlen + 64),
+                        max_slots=S + 1, dtype=bf, device=dev)
+        cache.groups[0].storage.normal_()
+        slots = [cache.acquire() for _ in range(S)]
+        for s_ in slots:
+            G.give_pages(cache, s_, ctxlen + 1)
+        b1 = G.make_batch(dev, slots, [ctxlen] * S, [1] * S)
+        q_ = torch.randn(S, nh, hd, device=dev).to(bf)
+        o_ = torch.empty((S, nh * hd), dtype=bf, device=dev)
+        ms = _graph_ms(lambda: core.attention_decode(q_, cache.view(0), b1, o_, nh=nh, window=window, scale=0.1, status=status, **kw))
+        read = min(window or ctxlen + 1, ctxlen + 1)
+        return ms, S * read * nkv * hd * 2 * (1 if latent else 2)
+
+    ms, nb = decode_case(LH, 1, rk, None, True, sink=sinks)
+    row("decode attention over latents (one record a position)", ms, nb)
+    ms, nb = decode_case(nh2, nkv2, D, win, False, softcap=sh["softcap"])
+    row("decode attention, two maps a head (window)", ms, nb)
+    ms, nb = decode_case(H, Gk, 2 * d, None, False)
+    row("decode attention, causal", ms, nb)
+    ms, nb = decode_case(H, Gk, 2 * d, win, False)
+    row("decode attention, window", ms, nb)
+    core.check_status(status)
+    return out
+
+
+def run_zosipel(args):
+    """``--workload zosipel``: prefill and decode of the Zosipel design at two sizes, the closest existing
+    model at equal size beside it, and the new kernels beside their counterparts.  One JSON line per
+    shape; not the benchmark record."""
+    import torch
+
+    import moe_b200
+
+    pk = peaks()
+    names = [args.shape] if args.shape in ZOSIPEL_SHAPES else list(ZOSIPEL_SHAPES)
+    for name in names:
+        sh = ZOSIPEL_SHAPES[name]
+        V = sh["vocab"]
+        res = {"workload": "zosipel", "shape": name, "sizes": sh, "dtype": "bfloat16", "data": "synthetic, random weights",
+               "peaks": pk}
+        for label, cfg in (("zosipel", zosipel_config(sh)), ("qwen2_moe", zosipel_qwen_config(sh))):
+            model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            r = {"parameters": int(model.num_parameters)}
+            eng = moe_b200.Engine(model, max_tokens=64 * (512 + args.steps + 64) + 4096, max_slots=64)
+            ids = [(i * 7 + 13) % V for i in range(PREFILL_TOKENS)]
+
+            def prefill():
+                s = eng.new_sequence()
+                eng.step([s], [ids], check=False)
+                eng.release(s)
+
+            ms = _median_ms(prefill)
+            r["prefill_2048"] = {"ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3, 0)}
+            for B in (1, 8, 64):
+                slots = [eng.new_sequence() for _ in range(B)]
+                eng.step(slots, [ids[:PROMPT_LEN]] * B, check=False)
+                for i in range(args.warmup):
+                    eng.step(slots, [[i % V]] * B, check=False)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for i in range(args.steps):
+                    eng.step(slots, [[(i + 5) % V]] * B, check=False)
+                b.record()
+                torch.cuda.synchronize()
+                eng.rt.check()
+                ms = a.elapsed_time(b) / args.steps
+                r[f"decode_b{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 0)}
+                for s in slots:
+                    eng.release(s)
+            res[label] = r
+            del eng, model
+            torch.cuda.empty_cache()
+        res["kernels_at_8192_tokens"] = zosipel_kernels(sh, pk)
+        print(json.dumps(res), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -838,12 +1095,12 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="with --profile-step: the path whose kernels are wanted")
-    ap.add_argument("--shape", choices=["a2.7b", "57b"] + sorted(set(SUPEVIK_SHAPES) | set(FOGAPEL_SHAPES)), default="a2.7b",
-                    help="with --sweep: the layer sizes; with --workload supevik or fogapel: one of its shapes (default: all)")
+    ap.add_argument("--shape", choices=["a2.7b", "57b"] + sorted(set(SUPEVIK_SHAPES) | set(FOGAPEL_SHAPES) | set(ZOSIPEL_SHAPES)), default="a2.7b",
+                    help="with --sweep: the layer sizes; with --workload supevik, fogapel or zosipel: one of its shapes (default: all)")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
-    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt", "supevik", "fogapel"], default=None,
+    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt", "supevik", "fogapel", "zosipel"], default=None,
                     help="fp32-32k: the true 32-bit path at a context of 32,768; long-prompt: one bfloat16 prompt of "
-                         "--prompt-len tokens [32768] run in pieces; supevik, fogapel: that design at two sizes beside "
+                         "--prompt-len tokens [32768] run in pieces; supevik, fogapel, zosipel: that design at two sizes beside "
                          "the closest model at equal size (each prints its own line, no benchmark record)")
     ap.add_argument("--unequal", action="store_true", help="with --sweep: prompts of unequal lengths, 256 to 2,048 tokens")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
@@ -867,6 +1124,8 @@ def main():
         return run_supevik(args)
     if args.workload == "fogapel":
         return run_fogapel(args)
+    if args.workload == "zosipel":
+        return run_zosipel(args)
     return run_ours(args)
 
 

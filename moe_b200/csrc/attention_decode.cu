@@ -23,6 +23,10 @@
 
 #include "common.cuh"
 
+// The tensor-core kernel for groups of many heads on or off (on by default; tests compare the two).
+static int g_decode_grouped = 1;
+static inline int moe_decode_grouped_enabled() { return g_decode_grouped; }
+
 namespace {
 
 constexpr int MAX_HD = 256;
@@ -574,6 +578,260 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, T* _
     }
 }
 
+
+// ---- many query heads on one key/value head: the scores and the weighted sum on the tensor cores ----
+// A group of eight and more query heads (attention over one latent record a position has ALL heads on
+// one record) makes the FFMA kernels above read every key once per pair of heads and spend
+// 2 x heads x head size multiply-adds a key on the CUDA cores.  Here the group's heads are the 16 rows
+// of an mma.sync m16n8k16 tile (bfloat16 inputs, 32-bit accumulation; heads beyond the group are rows
+// of zeros): a block of four warps takes (key split, kv head, 16 heads, token), stages tiles of 64 keys
+// (one page: contiguous in the cache) through shared memory with cp.async, two buffers, and every warp
+// owns 16 keys of a tile with a running maximum, sum and output of its own; the four are merged at the
+// end and leave the same partial record as the kernels above, so the merge kernel is shared.  Scores,
+// cap, softmax and sums are 32-bit; the softmax weights enter the second product as two bfloat16 terms
+// (16 bits).  Where the values are the keys (one plane) the tile is staged once.
+constexpr int GT_KEYS = 64, GT_HEADS = 16;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attn_decode_grouped_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                           const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ partial,
+                           const int* __restrict__ seq_of_token, const int* __restrict__ pos,
+                           const int* __restrict__ slots, const int* __restrict__ tables, int table_stride, int ring,
+                           int num_pages, int nh, int nkv, int window, float scale, int* status, const AttnVariant av) {
+    constexpr int ROW = HD * 2 + 16;                     // bytes of a staged row: ldmatrix without bank conflicts
+    constexpr int CPR = HD * 2 / 16;                     // 16-byte chunks of a row
+    constexpr int REC = HD + 2;
+    extern __shared__ __align__(16) unsigned char gsm[];
+    const bool shared_kv = (k_cache == v_cache);
+    const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(gsm);
+    const uint32_t sK = sQ + GT_HEADS * ROW;             // two buffers
+    const uint32_t sV = shared_kv ? sK : sK + 2 * GT_KEYS * ROW;
+    const int group = nh / nkv;
+    const int htiles = (group + GT_HEADS - 1) / GT_HEADS;
+    const int split = blockIdx.x, nsplit = gridDim.x, kvh = blockIdx.y / htiles, t = blockIdx.z;
+    const int h0 = (blockIdx.y % htiles) * GT_HEADS;
+    const int gh = min(GT_HEADS, group - h0);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s = seq_of_token[t];
+    pdl_sync();
+    if (s < 0) return;                                   // a row of no sequence: the merge writes zeros
+    const int p = pos[t];
+    const int lo = attn_lo(p, window, av.chunk);
+    const int tile_lo = lo / GT_KEYS, tile_hi = p / GT_KEYS + 1;
+    const int tps = (tile_hi - tile_lo + nsplit - 1) / nsplit;
+    const int tb = tile_lo + split * tps, te = min(tile_hi, tb + tps);
+    const int* table = tables + (size_t)slots[s] * table_stride;
+
+    // the group's queries: 16 rows, zeros beyond the group
+    for (int c = threadIdx.x; c < GT_HEADS * CPR; c += WARPS * 32) {
+        const int r = c / CPR, ch = c % CPR;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < gh) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * nh + kvh * group + h0 + r) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(gsm + r * ROW + ch * 16) = v;
+    }
+    auto load_tile = [&](int tile, int buf) {
+        const CachePos cp = cache_pos(tile * GT_KEYS, ring, table, GT_KEYS, num_pages, status);
+        const size_t at = cache_index(cp, kvh, nkv, GT_KEYS, HD);
+        for (int c = threadIdx.x; c < GT_KEYS * CPR; c += WARPS * 32) {
+            const int r = c / CPR, ch = c % CPR;
+            cp_async16(sK + (buf * GT_KEYS + r) * ROW + ch * 16, k_cache + at + (size_t)r * HD + ch * 8);
+            if (!shared_kv) cp_async16(sV + (buf * GT_KEYS + r) * ROW + ch * 16, v_cache + at + (size_t)r * HD + ch * 8);
+        }
+        cp_async_commit();
+    };
+    if (tb < te) load_tile(tb, 0);
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++)
+        ldsm_x4(sQ + (lane & 15) * ROW + ks * 32 + (lane >> 4) * 16, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int tile = tb; tile < te; tile++) {
+        const int buf = (tile - tb) & 1;
+        if (tile + 1 < te) {
+            load_tile(tile + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t kb = sK + buf * GT_KEYS * ROW, vb = sV + buf * GT_KEYS * ROW;
+        const int j0 = tile * GT_KEYS + warp * 16;       // this warp's 16 keys
+        if (j0 <= p && j0 + 15 >= lo) {                   // (warp-uniform) some of them are seen
+            float sc[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ks++) {
+                uint32_t b0, b1, b2, b3;
+                const int r = warp * 16 + (lane & 7) + ((lane >> 4) << 3), cb = ks * 32 + ((lane >> 3) & 1) * 16;
+                ldsm_x4(kb + r * ROW + cb, b0, b1, b2, b3);
+                mma_bf16(sc[0], qf[ks], b0, b1);
+                mma_bf16(sc[1], qf[ks], b2, b3);
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int j = j0 + i * 8 + (lane & 3) * 2 + (e & 1);
+                    const float x = (j >= lo && j <= p) ? attn_score(sc[i][e], scale, av.softcap) : -INFINITY;
+                    sc[i][e] = x;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], x);
+                }
+            }
+            float alpha[2];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m[h], mx[h]);
+                alpha[h] = (m[h] == -INFINITY) ? 0.f : expf(m[h] - m_new);
+                m[h] = m_new;
+            }
+            float rs[2] = {0.f, 0.f};
+            uint32_t pf[4], pr[4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                float pv[4], rem[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float mm = m[e >> 1];
+                    pv[e] = (mm == -INFINITY) ? 0.f : expf(sc[i][e] - mm);
+                    rs[e >> 1] += pv[e];
+                    rem[e] = pv[e] - __bfloat162float(__float2bfloat16_rn(pv[e]));
+                }
+                pf[i * 2] = pack_bf16(pv[0], pv[1]), pf[i * 2 + 1] = pack_bf16(pv[2], pv[3]);
+                pr[i * 2] = pack_bf16(rem[0], rem[1]), pr[i * 2 + 1] = pack_bf16(rem[2], rem[3]);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 1);
+                rs[h] += __shfl_xor_sync(0xffffffffu, rs[h], 2);
+                l[h] = l[h] * alpha[h] + rs[h];
+            }
+#pragma unroll
+            for (int i = 0; i < HD / 8; i++) {
+                o[i][0] *= alpha[0], o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1], o[i][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; dp++) {
+                uint32_t b0, b1, b2, b3;
+                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, cb = dp * 32 + (lane >> 4) * 16;
+                ldsm_x4_t(vb + r * ROW + cb, b0, b1, b2, b3);
+                mma_bf16(o[2 * dp], pf, b0, b1);
+                mma_bf16(o[2 * dp + 1], pf, b2, b3);
+                mma_bf16(o[2 * dp], pr, b0, b1);
+                mma_bf16(o[2 * dp + 1], pr, b2, b3);
+            }
+        }
+        __syncthreads();                                  // this buffer is refilled two tiles on
+    }
+
+    // ---- the four warps' results into one record a head (the staging buffers are free now) ----------
+    float* red = reinterpret_cast<float*>(gsm);           // [WARPS][16][REC]
+    __syncthreads();
+    {
+        const int ra = lane >> 2, rb = ra + 8;
+        float* wa = red + ((size_t)warp * GT_HEADS + ra) * REC;
+        float* wb = red + ((size_t)warp * GT_HEADS + rb) * REC;
+#pragma unroll
+        for (int i = 0; i < HD / 8; i++) {
+            const int d = i * 8 + (lane & 3) * 2;
+            wa[d] = o[i][0], wa[d + 1] = o[i][1];
+            wb[d] = o[i][2], wb[d + 1] = o[i][3];
+        }
+        if ((lane & 3) == 0) {
+            wa[HD] = m[0], wa[HD + 1] = l[0];
+            wb[HD] = m[1], wb[HD + 1] = l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < gh * HD; idx += WARPS * 32) {
+        const int g = idx / HD, d = idx % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) mm = fmaxf(mm, red[((size_t)w * GT_HEADS + g) * REC + HD]);
+        float a = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) {
+            const float* rw = red + ((size_t)w * GT_HEADS + g) * REC;
+            const float f = (rw[HD] == -INFINITY) ? 0.f : expf(rw[HD] - mm);
+            a += f * rw[d];
+            ll += f * rw[HD + 1];
+        }
+        float* out = partial + (((size_t)t * nh + kvh * group + h0 + g) * nsplit + split) * REC;
+        out[d] = a;
+        if (d == 0) out[HD] = mm, out[HD + 1] = ll;
+    }
+}
+
+// Heads of a group at or above which the tensor-core kernel above takes a bfloat16 step.
+constexpr int GROUPED_MIN_HEADS = 8;
+
+template <int HD>
+int launch_grouped(const void* q, const void* k_cache, const void* v_cache, float* partial, const int* seq_of_token,
+                   const int* pos, const int* slots, const int* tables, int table_stride, int ring, int num_pages,
+                   int num_tokens, int nh, int nkv, int window, float scale, int nsplit, int* status,
+                   cudaStream_t stream, const AttnVariant av) {
+    constexpr int ROW = HD * 2 + 16;
+    const bool shared_kv = k_cache == v_cache;
+    const size_t stage = (size_t)(GT_HEADS + (shared_kv ? 2 : 4) * GT_KEYS) * ROW;
+    const size_t merge = (size_t)WARPS * GT_HEADS * (HD + 2) * sizeof(float);
+    const size_t smem = stage > merge ? stage : merge;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_grouped_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)((size_t)(GT_HEADS + 4 * GT_KEYS) * ROW > merge
+                                                       ? (size_t)(GT_HEADS + 4 * GT_KEYS) * ROW : merge));
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int group = nh / nkv;
+    dim3 grid(nsplit, nkv * ((group + GT_HEADS - 1) / GT_HEADS), num_tokens);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    return launch_pdl(attn_decode_grouped_kernel<HD>, grid, WARPS * 32, smem, stream, (const __nv_bfloat16*)q,
+                      (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, partial, seq_of_token, pos, slots,
+                      tables, table_stride, ring, num_pages, nh, nkv, window, scale, status, av);
+}
+
 // Bytes of keys and values that the blocks of one launch may ask for in L2 ahead of their wait:
 // a quarter of the device's L2.
 int l2_prefetch_bytes() {
@@ -604,6 +862,21 @@ int launch(const void* q, const void* k_cache, const void* v_cache, void* out, f
     const bool fast = aligned && page_size % 32 == 0 && (ring % 32 == 0) &&
                       (row_bytes == 64 || row_bytes == 128 || row_bytes == 256 || row_bytes == 512);
     if (fused && !fast) return -1;
+    if constexpr (sizeof(T) == 2) {
+        // many heads on one key/value head: scores and weighted sum on the tensor cores
+        if (!fused && aligned && group >= GROUPED_MIN_HEADS && (hd == 64 || hd == 128) && page_size == GT_KEYS &&
+            ring % GT_KEYS == 0 && moe_decode_grouped_enabled()) {
+            const int rc = hd == 64 ? launch_grouped<64>(q, k_cache, v_cache, partial, seq_of_token, pos, slots, tables,
+                                                        table_stride, ring, num_pages, num_tokens, nh, nkv, window, scale,
+                                                        nsplit, status, stream, av)
+                                    : launch_grouped<128>(q, k_cache, v_cache, partial, seq_of_token, pos, slots, tables,
+                                                         table_stride, ring, num_pages, num_tokens, nh, nkv, window, scale,
+                                                         nsplit, status, stream, av);
+            if (rc) return rc;
+            return launch_pdl(attn_decode_merge_kernel<T>, dim3(num_tokens, nh), 128, 0, stream, (const float*)partial,
+                              (T*)out, seq_of_token, nh, hd, nsplit, go, av);
+        }
+    }
     const FusedArgs fa = fused ? *fused : FusedArgs{};
     const int budget = l2_prefetch_bytes();
 #define FAST(LPR, GH)                                                                                             \
@@ -679,6 +952,8 @@ MOE_API int moe_attention_decode_fused(const float* qkv, const float* inv_freq, 
                                  table_stride, ring, page_size, num_pages, num_tokens, nh, nkv, hd, window, scale,
                                  nsplit, status, stream, &fa);
 }
+
+MOE_API void moe_set_decode_grouped(int enabled) { g_decode_grouped = enabled ? 1 : 0; }
 
 // q: [T, nh, hd]; out: [T, nh * hd]; partial: T * nh * nsplit * (hd + 2) floats of scratch.
 // With dv > 0 out is [T, nh * dv]: the first dv columns of every head, times the sigmoid of the

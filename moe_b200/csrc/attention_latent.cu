@@ -35,13 +35,33 @@ struct LatentCommit {
     int table_stride, ring, page_size, num_pages;
 };
 
+// four consecutive elements at once (the pointer is aligned to four elements)
+__device__ __forceinline__ void ld4(const float* p, float* v) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x, v[1] = x.y, v[2] = x.z, v[3] = x.w;
+}
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float* v) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(x.x << 16), v[1] = __uint_as_float(x.x & 0xffff0000u);
+    v[2] = __uint_as_float(x.y << 16), v[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+__device__ __forceinline__ void st4(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float* v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 x;
+    x.x = *reinterpret_cast<const unsigned*>(&a), x.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = x;
+}
+
 // One block a token.
 template <typename OT>
 __global__ void __launch_bounds__(256)
 latent_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restrict__ pos,
                       const int* __restrict__ seq_of_token, const float* __restrict__ w, float eps, int num_tokens,
                       int nh, int d, int r, int D, OT* __restrict__ q_t, OT* __restrict__ k_new,
-                      const LatentCommit c, int* status) {
+                      const LatentCommit c, int* status, int vec4) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     pdl_sync();
@@ -71,27 +91,61 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restr
         if (cd) st_f(cd + i, x);
         if (cv) st_f(cv + i, x);
     }
+    if (vec4) {          // d and the row pitch are multiples of four, both pointers aligned to four elements
+        for (int i = threadIdx.x * 4; i < nh * d; i += blockDim.x * 4) {
+            const int h = i / d, j = i % d;
+            float v[4];
+            ld4(row + i, v);
+            st4(q_t + ((size_t)h * num_tokens + t) * d + j, v);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < nh * d; i += blockDim.x) {
         const int h = i / d, j = i % d;
         st_f(q_t + ((size_t)h * num_tokens + t) * d + j, row[i]);
     }
 }
 
-template <typename ST, typename DT>
+__device__ __forceinline__ void ld2(const float* p, float* v) {
+    const float2 x = *reinterpret_cast<const float2*>(p);
+    v[0] = x.x, v[1] = x.y;
+}
+__device__ __forceinline__ void ld2(const __nv_bfloat16* p, float* v) {
+    const unsigned x = *reinterpret_cast<const unsigned*>(p);
+    v[0] = __uint_as_float(x << 16), v[1] = __uint_as_float(x & 0xffff0000u);
+}
+__device__ __forceinline__ void st2(float* p, const float* v) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+__device__ __forceinline__ void st2(__nv_bfloat16* p, const float* v) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+}
+
+// VEC = 4: n, wd and both pitches are multiples of four and both pointers aligned to four elements.
+template <typename ST, typename DT, int VEC>
 __global__ void heads_transpose_kernel(const ST* __restrict__ src, long long s_outer, long long s_inner, int A, int B,
                                        int n, int wd, DT* __restrict__ dst) {
     pdl_sync();
-    const long long total = (long long)A * B * wd;
+    const int wv = wd / VEC;
+    const long long total = (long long)A * B * wv;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const int j = (int)(i % wd);
-    const long long ba = i / wd;
+    const int j = (int)(i % wv) * VEC;
+    const long long ba = i / wv;
     const int a = (int)(ba % A), b = (int)(ba / A);
-    st_f(dst + i, j < n ? ld_f(src + (size_t)a * s_outer + (size_t)b * s_inner + j) : 0.f);
+    const ST* from = src + (size_t)a * s_outer + (size_t)b * s_inner + j;
+    DT* to = dst + ba * wd + j;
+    if (VEC == 4) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (j < n) ld4(from, v);
+        st4(to, v);
+    } else {
+        st_f(to, j < n ? ld_f(from) : 0.f);
+    }
 }
 
-// One warp a (token, head).
-template <typename T>
+// One warp a (token, head).  The head's difference stays in registers between the norm's sum and the
+// store (dv <= 256: up to eight elements a lane); with an even dv (and 4-byte aligned rows) a lane
+// takes two neighbouring elements a load.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(128)
 diff_combine_kernel(const T* __restrict__ ctx, const float* __restrict__ gate, int gate_ld, long long pairs, int nh,
                     int dv, int D, float lambda, float eps, float mult, T* __restrict__ out) {
@@ -103,16 +157,42 @@ diff_combine_kernel(const T* __restrict__ ctx, const float* __restrict__ gate, i
     const int h = (int)(w % nh);
     const T* a1 = ctx + ((size_t)t * 2 * nh + h) * D;
     const T* a2 = ctx + ((size_t)t * 2 * nh + nh + h) * D;
+    constexpr int SLOTS = 256 / (32 * VEC);
+    float o[SLOTS][VEC];
     float ss = 0.f;
-    for (int j = lane; j < dv; j += 32) {
-        const float o = ld_f(a1 + j) - lambda * ld_f(a2 + j);
-        ss += o * o;
+#pragma unroll
+    for (int i = 0; i < SLOTS; i++) {
+        const int j = (i * 32 + lane) * VEC;
+#pragma unroll
+        for (int e = 0; e < VEC; e++) o[i][e] = 0.f;
+        if (j < dv) {
+            if (VEC == 2) {
+                float x[2], y[2];
+                ld2(a1 + j, x), ld2(a2 + j, y);
+                o[i][0] = x[0] - lambda * y[0], o[i][1] = x[1] - lambda * y[1];
+            } else {
+                o[i][0] = ld_f(a1 + j) - lambda * ld_f(a2 + j);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; e++) ss += o[i][e] * o[i][e];
     }
     ss = warp_sum(ss);
     float f = mult / sqrtf(ss / (float)dv + eps);
     if (gate) f *= 1.0f / (1.0f + expf(-gate[(size_t)t * gate_ld + h]));
     T* o_row = out + ((size_t)t * nh + h) * dv;
-    for (int j = lane; j < dv; j += 32) st_f(o_row + j, (ld_f(a1 + j) - lambda * ld_f(a2 + j)) * f);
+#pragma unroll
+    for (int i = 0; i < SLOTS; i++) {
+        const int j = (i * 32 + lane) * VEC;
+        if (j < dv) {
+            if (VEC == 2) {
+                const float v[2] = {o[i][0] * f, o[i][1] * f};
+                st2(o_row + j, v);
+            } else {
+                st_f(o_row + j, o[i][0] * f);
+            }
+        }
+    }
 }
 
 __global__ void add_row_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ row,
@@ -138,11 +218,13 @@ MOE_API int moe_latent_prepare(const float* proj, int ld, const int* pos, const 
         return (int)cudaErrorInvalidValue;
     if (k_cache && (!seq_end || !slots || !tables || !seq_of_token || !pos)) return (int)cudaErrorInvalidValue;
     const LatentCommit c{k_cache, v_cache, seq_end, slots, tables, table_stride, ring, page_size, num_pages};
+    const int vec4 = d % 4 == 0 && ld % 4 == 0 && (uintptr_t)proj % 16 == 0 &&
+                     (uintptr_t)q_t % (out_dt == DT_F32 ? 16 : 8) == 0;
     if (out_dt == DT_F32)
         return launch_pdl(latent_prepare_kernel<float>, num_tokens, 256, 0, stream, proj, ld, pos, seq_of_token, w, eps,
-                          num_tokens, nh, d, r, D, (float*)q_t, (float*)k_new, c, status);
+                          num_tokens, nh, d, r, D, (float*)q_t, (float*)k_new, c, status, vec4);
     return launch_pdl(latent_prepare_kernel<__nv_bfloat16>, num_tokens, 256, 0, stream, proj, ld, pos, seq_of_token, w,
-                      eps, num_tokens, nh, d, r, D, (__nv_bfloat16*)q_t, (__nv_bfloat16*)k_new, c, status);
+                      eps, num_tokens, nh, d, r, D, (__nv_bfloat16*)q_t, (__nv_bfloat16*)k_new, c, status, vec4);
 }
 
 // src: element (a, b, j) at a * s_outer + b * s_inner + j, j < n; dst: dense [B, A, wd].
@@ -151,10 +233,15 @@ MOE_API int moe_heads_transpose(const void* src, int src_dt, long long s_outer, 
     const long long total = (long long)A * B * wd;
     if (total <= 0) return 0;
     if (n < 0 || n > wd || !src || !dst) return (int)cudaErrorInvalidValue;
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-#define TR(ST_, DT_)                                                                                              \
-    return launch_pdl(heads_transpose_kernel<ST_, DT_>, blocks, 256, 0, stream, (const ST_*)src, s_outer, s_inner, A, B, \
-                      n, wd, (DT_*)dst)
+    const size_t se = src_dt == DT_F32 ? 4 : 2, de = dst_dt == DT_F32 ? 4 : 2;
+    const bool vec = n % 4 == 0 && wd % 4 == 0 && s_outer % 4 == 0 && s_inner % 4 == 0 &&
+                     (uintptr_t)src % (4 * se) == 0 && (uintptr_t)dst % (4 * de) == 0;
+    const unsigned blocks = (unsigned)(((vec ? total / 4 : total) + 255) / 256);
+#define TR(ST_, DT_)                                                                                                \
+    return vec ? launch_pdl(heads_transpose_kernel<ST_, DT_, 4>, blocks, 256, 0, stream, (const ST_*)src, s_outer,      \
+                            s_inner, A, B, n, wd, (DT_*)dst)                                                        \
+               : launch_pdl(heads_transpose_kernel<ST_, DT_, 1>, blocks, 256, 0, stream, (const ST_*)src, s_outer,      \
+                            s_inner, A, B, n, wd, (DT_*)dst)
     if (src_dt == DT_F32) {
         if (dst_dt == DT_F32) TR(float, float);
         TR(float, __nv_bfloat16);
@@ -171,12 +258,20 @@ MOE_API int moe_diff_combine(const void* ctx, const float* gate, int gate_ld, in
     const long long pairs = (long long)num_tokens * nh;
     if (pairs <= 0) return 0;
     if (dv <= 0 || D < dv || !ctx || !out) return (int)cudaErrorInvalidValue;
+    if (dv > 256) return (int)cudaErrorInvalidValue;
     const unsigned blocks = (unsigned)((pairs + 3) / 4);
-    if (dt == DT_F32)
-        return launch_pdl(diff_combine_kernel<float>, blocks, 128, 0, stream, (const float*)ctx, gate, gate_ld, pairs,
-                          nh, dv, D, lambda, eps, mult, (float*)out);
-    return launch_pdl(diff_combine_kernel<__nv_bfloat16>, blocks, 128, 0, stream, (const __nv_bfloat16*)ctx, gate,
-                      gate_ld, pairs, nh, dv, D, lambda, eps, mult, (__nv_bfloat16*)out);
+    const size_t el = dt == DT_F32 ? 4 : 2;
+    const bool vec = dv % 2 == 0 && D % 2 == 0 && (uintptr_t)ctx % (2 * el) == 0 && (uintptr_t)out % (2 * el) == 0;
+#define DC(T_, V_)                                                                                                 \
+    return launch_pdl(diff_combine_kernel<T_, V_>, blocks, 128, 0, stream, (const T_*)ctx, gate, gate_ld, pairs, nh, dv, \
+                      D, lambda, eps, mult, (T_*)out)
+    if (dt == DT_F32) {
+        if (vec) DC(float, 2);
+        DC(float, 1);
+    }
+    if (vec) DC(__nv_bfloat16, 2);
+    DC(__nv_bfloat16, 1);
+#undef DC
 }
 
 MOE_API int moe_add_row(float* x, const float* delta, const float* row, long long num_tokens, int width,

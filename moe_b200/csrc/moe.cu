@@ -545,6 +545,7 @@ struct NormRouteParams {
     int* status;
     int vec_ok;
     int cluster;              // 1: the tokens' blocks are one cluster (at most 8 tokens), see the kernel
+    int groups, keep;         // experts picked within the best `keep` of `groups` groups (0: no groups)
 };
 
 template <typename WT>
@@ -641,7 +642,7 @@ __global__ void __launch_bounds__(1024) norm_route_kernel(const NormRouteParams 
     if (warp == 0)
         route_token(logit, sc, lane, p.seq_of_token && p.seq_of_token[t] < 0, E, p.rows, p.top_k, p.norm_topk, p.scale,
                     p.topk_idx + (size_t)t * p.top_k, p.topk_w + (size_t)t * p.top_k,
-                    p.shared_gate ? p.shared_gate + t : nullptr, wk);
+                    p.shared_gate ? p.shared_gate + t : nullptr, wk, nullptr, p.groups, p.keep);
 
     if (p.cluster) {
         // ---- one cluster: every block learns all picks through distributed shared memory, inverts
@@ -797,9 +798,11 @@ MOE_API int moe_norm_route(float* x, const float* delta, const float* norm_w, fl
                            float* out32, void* out16, const void* wr, const void* wsg, int w_dt, int num_experts,
                            int top_k, int norm_topk, float scale, const int* seq_of_token, int* topk_idx,
                            float* topk_w, float* shared_gate, int* offsets, int* sorted_token, int* pos_of_pair,
-                           void* xs, int* ticket, int* status, cudaStream_t stream) {
+                           void* xs, int* ticket, int* status, int groups, int keep, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (top_k <= 0 || top_k > num_experts || hidden <= 0 || !ticket || (wsg && !shared_gate) || (xs && !out16))
+        return (int)cudaErrorInvalidValue;
+    if (groups > 1 && (num_experts % groups || keep < 1 || keep > groups || top_k > keep * (num_experts / groups)))
         return (int)cudaErrorInvalidValue;
     const int pairs = num_tokens * top_k;
     if (num_tokens > 64 || num_experts > 256 || pairs > 4096) return -1;
@@ -810,6 +813,7 @@ MOE_API int moe_norm_route(float* x, const float* delta, const float* norm_w, fl
     p.seq_of_token = seq_of_token, p.topk_idx = topk_idx, p.topk_w = topk_w, p.shared_gate = shared_gate;
     p.offsets = offsets, p.sorted_token = sorted_token, p.pos_of_pair = pos_of_pair;
     p.xs = (uint4*)xs, p.row_units = hidden * 2 / 16, p.ticket = ticket, p.status = status;
+    p.groups = groups, p.keep = keep;
     if (xs && ((hidden * 2) % 16 || (uintptr_t)xs % 16 || (uintptr_t)out16 % 16)) return -1;
     const size_t elt = w_dt == DT_F32 ? 4 : 2;
     p.vec_ok = (hidden % 8 == 0) && ((uintptr_t)wr % 16 == 0) && (!wsg || (uintptr_t)wsg % 16 == 0) &&

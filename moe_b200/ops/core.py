@@ -64,7 +64,7 @@ def lib():
             "moe_wkv_finish": [P, P, LL, P, F, P, I, I, I, P, I, P],
             "moe_rmsnorm_scaled": [P, P, P, P, P, P, P, P, P, I, I, I, F, I, P, P, P, P, I, P, P],
             "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
-            "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, P],
+            "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, I, I, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
             "moe_swiglu": [P, P, I, LL, I, I, F, P],
             "moe_combine": [P, P, P, I, P, P, P, I, I, P],
@@ -85,6 +85,8 @@ def lib():
             L.moe_set_pdl(0)
         L.moe_set_norm_route_cluster.argtypes = [c_int]
         L.moe_set_norm_route_cluster.restype = None
+        L.moe_set_decode_grouped.argtypes = [c_int]
+        L.moe_set_decode_grouped.restype = None
         if os.environ.get("MOE_B200_NORM_ROUTE_CLUSTER", "1") == "0":   # ticket form also for few tokens
             L.moe_set_norm_route_cluster(0)
         _lib = L
@@ -798,9 +800,14 @@ def decode_splits(device, num_tokens: int, nkv: int, max_end: int = 0) -> int:
     return n
 
 
-def _head_blocks(nh: int, nkv: int) -> int:
-    """Blocks along the heads of the decode attention's grid: a kv head's query heads two at a time."""
+def _head_blocks(nh: int, nkv: int, group_view=None, dtype=None) -> int:
+    """Blocks along the heads of the decode attention's grid: a kv head's query heads two at a time, or,
+    where the tensor-core kernel for groups of eight and more heads takes the step (bfloat16, records of
+    64 or 128, pages of 64), sixteen at a time."""
     group = max(1, nh // max(nkv, 1))
+    if (group_view is not None and dtype == torch.bfloat16 and group >= 8 and group_view.head_dim in (64, 128)
+            and group_view.page_size == 64 and group_view.ring % 64 == 0):
+        return nkv * -(-group // 16)
     return nkv * (1 if group == 1 else -(-group // 2))
 
 
@@ -830,7 +837,7 @@ def attention_decode(q, view, batch, out, *, nh, window, scale, status, gate=Non
     if q.dtype != g.dtype or out.dtype != q.dtype:
         raise KernelError("attention: dtypes of queries, cache and output must agree")
     gp, gld, gdv = _gate_args(out, T, nh, g.head_dim, gate, dv)
-    nsplit = decode_splits(q.device, T, _head_blocks(nh, g.num_kv_heads), getattr(batch, "max_end", 0))
+    nsplit = decode_splits(q.device, T, _head_blocks(nh, g.num_kv_heads, g, q.dtype), getattr(batch, "max_end", 0))
     partial = torch.empty(T * nh * nsplit * (g.head_dim + 2), dtype=torch.float32, device=q.device)
     _ok(lib().moe_attention_decode(_p(q), _p(view.k), _p(view.v), _p(out), _p(partial), _dt(q),
                                    _p(batch.seq_of_token), _p(batch.pos), _p(batch.slots), _p(g.table),
@@ -984,7 +991,7 @@ def rope_commit(qkv, pos, inv_freq, nh, nkv, hd, rot, q, view, batch, status):
 
 
 def norm_route(x, delta, norm_w, eps, w_router, top_k, norm_topk, scale, *, bf16, shared_gate_w=None,
-               seq_of_token=None, status=None):
+               seq_of_token=None, status=None, groups=0, keep=0):
     """Few tokens: ``x += delta``, RMS norm, router logits, pick, table inversion and gather of the
     normalised bfloat16 rows in ONE launch.  Returns None (nothing launched) for sizes the kernel
     does not take, else (out32 or None, out16 or None, topk_idx, topk_w, shared_gate, offsets,
@@ -1009,7 +1016,7 @@ def norm_route(x, delta, norm_w, eps, w_router, top_k, norm_topk, scale, *, bf16
     code = lib().moe_norm_route(_p(x), _p(delta), _p(norm_w), float(eps), H, T, _p(out32), _p(out16), _p(w_router),
                                 _p(shared_gate_w), _dt(w_router), E, top_k, 1 if norm_topk else 0, float(scale),
                                 _p(seq_of_token), _p(topk_idx), _p(topk_w), _p(sg), _p(offsets), _p(sorted_token),
-                                _p(pos_of_pair), _p(xs), _p(ticket), _p(status), _stream())
+                                _p(pos_of_pair), _p(xs), _p(ticket), _p(status), int(groups), int(keep), _stream())
     if code == -1:
         return None
     _ok(code, "norm_route")

@@ -82,6 +82,10 @@ CONFIGS = {
               moe(8, 2, 64, 64, groups=(4, 2))),
         layer(latent(4, 32, 48, 128, scale=0.15), moe(4, 2, 48, 0)),
         layer(latent(2, 64, 64, 64, scale=0.125), None)]),
+    # one windowed layer with part of a map unrotated: the tests make one key stand out in it, whatever
+    # the distance to the query, and move the window's edge
+    "edge": dict(vocab=90, width=64, eps=1e-5, loop=None, layers=[
+        layer(attention(4, 2, 32, 24, window=67, rot=16, scale=0.5, diff=0.3), moe(3, 1, 24, 16))]),
     # one latent layer, which sees everything: the tests make one far key stand out in it
     "far": dict(vocab=70, width=32, eps=1e-5, loop=None, layers=[
         layer(latent(2, 16, 16, 16, scale=1.0), moe(2, 1, 24, 0))]),
@@ -110,6 +114,33 @@ def spike_token(w, cfg, token):
         w["l0.mix.uk"][h * d, 0] = 4.0
         w["l0.mix.q"][h * d, :] = 0.0
         w["l0.mix.q"][h * d, 1] = 4.0
+
+
+def spike_attention(w, cfg, token):
+    """Change drawn weights of a model whose first layer is differential attention with an unrotated
+    last dimension in every map, so that in map 1 of every head every query looks at the key of
+    ``token`` while that key is in its window: only that token has a component along feature 0, which
+    alone feeds the last dimension of map 1 of every key head; every token has the same component
+    along feature 1, which alone feeds the last dimension of map 1 of every query head."""
+    m = cfg["layers"][0]["mixer"]
+    d = m["dim"]
+    assert m.get("rot") is None or m["rot"]["dims"] < d
+    w["embed"][:, 0] = 0.0
+    w["embed"][token, 0] = 8.0
+    w["embed"][:, 1] = 2.0
+    if "loop.step" in w:
+        w["loop.step"][:, :2] = 0.0
+    w["l0.norm1"][:2] = 0.0
+    w["l0.mix.k"][:, 0] = 0.0
+    w["l0.mix.q"][:, 0] = 0.0
+    for g in range(m["kv_heads"]):
+        row = g * 2 * d + d - 1
+        w["l0.mix.k"][row, :], w["l0.mix.k.b"][row] = 0.0, 0.0
+        w["l0.mix.k"][row, 0] = 4.0
+    for h in range(m["heads"]):
+        row = h * 2 * d + d - 1
+        w["l0.mix.q"][row, :], w["l0.mix.q.b"][row] = 0.0, 0.0
+        w["l0.mix.q"][row, 1] = 4.0
 
 
 def config_dict(name):
