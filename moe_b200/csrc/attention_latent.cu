@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(256)
 latent_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restrict__ pos,
                       const int* __restrict__ seq_of_token, const float* __restrict__ w, float eps, int num_tokens,
                       int nh, int d, int r, int D, OT* __restrict__ q_t, OT* __restrict__ k_new,
-                      const LatentCommit c, int* status, int vec4) {
+                      const LatentCommit c, int* status, int vec4, int q_major) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     pdl_sync();
@@ -90,6 +90,23 @@ latent_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restr
         st_f(kd + i, x);
         if (cd) st_f(cd + i, x);
         if (cv) st_f(cv + i, x);
+    }
+    if (q_major) {       // the queries token by token, q[t][h][0..D), zero-filled beyond d
+        OT* qd = q_t + (size_t)t * nh * D;
+        if (vec4 && D % 4 == 0) {
+            for (int i = threadIdx.x * 4; i < nh * D; i += blockDim.x * 4) {
+                const int h = i / D, j = i % D;
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                if (j < d) ld4(row + (size_t)h * d + j, v);
+                st4(qd + i, v);
+            }
+        } else {
+            for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+                const int h = i / D, j = i % D;
+                st_f(qd + i, j < d ? row[(size_t)h * d + j] : 0.f);
+            }
+        }
+        return;
     }
     if (vec4) {          // d and the row pitch are multiples of four, both pointers aligned to four elements
         for (int i = threadIdx.x * 4; i < nh * d; i += blockDim.x * 4) {
@@ -207,14 +224,15 @@ __global__ void add_row_kernel(float* __restrict__ x, const float* __restrict__ 
 
 }  // namespace
 
-// proj: [T, ld] 32-bit: nh * d query columns, then r latent columns.  q_t: [nh, T, d]; k_new: [T, D].
+// proj: [T, ld] 32-bit: nh * d query columns, then r latent columns.  q_t: [nh, T, d], or with q_major
+// [T, nh, D] zero-filled beyond d (d <= D); k_new: [T, D].
 MOE_API int moe_latent_prepare(const float* proj, int ld, const int* pos, const int* seq_of_token, const float* w,
                                float eps, int num_tokens, int nh, int d, int r, int D, void* q_t, void* k_new,
                                int out_dt, void* k_cache, void* v_cache, const int* seq_end, const int* slots,
                                const int* tables, int table_stride, int ring, int page_size, int num_pages,
-                               int* status, cudaStream_t stream) {
+                               int* status, int q_major, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    if (nh <= 0 || d <= 0 || r <= 0 || D < r || ld < nh * d + r || !proj || !w || !q_t || !k_new)
+    if (nh <= 0 || d <= 0 || r <= 0 || D < r || ld < nh * d + r || !proj || !w || !q_t || !k_new || (q_major && d > D))
         return (int)cudaErrorInvalidValue;
     if (k_cache && (!seq_end || !slots || !tables || !seq_of_token || !pos)) return (int)cudaErrorInvalidValue;
     const LatentCommit c{k_cache, v_cache, seq_end, slots, tables, table_stride, ring, page_size, num_pages};
@@ -222,9 +240,9 @@ MOE_API int moe_latent_prepare(const float* proj, int ld, const int* pos, const 
                      (uintptr_t)q_t % (out_dt == DT_F32 ? 16 : 8) == 0;
     if (out_dt == DT_F32)
         return launch_pdl(latent_prepare_kernel<float>, num_tokens, 256, 0, stream, proj, ld, pos, seq_of_token, w, eps,
-                          num_tokens, nh, d, r, D, (float*)q_t, (float*)k_new, c, status, vec4);
+                          num_tokens, nh, d, r, D, (float*)q_t, (float*)k_new, c, status, vec4, q_major);
     return launch_pdl(latent_prepare_kernel<__nv_bfloat16>, num_tokens, 256, 0, stream, proj, ld, pos, seq_of_token, w,
-                      eps, num_tokens, nh, d, r, D, (__nv_bfloat16*)q_t, (__nv_bfloat16*)k_new, c, status, vec4);
+                      eps, num_tokens, nh, d, r, D, (__nv_bfloat16*)q_t, (__nv_bfloat16*)k_new, c, status, vec4, q_major);
 }
 
 // src: element (a, b, j) at a * s_outer + b * s_inner + j, j < n; dst: dense [B, A, wd].

@@ -36,7 +36,7 @@ def lib():
             "moe_dyt": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
             "moe_heads_prepare": [P, I, P, P, P, P, F, P, I, F, I, I, I, I, I, I, P, P, P, LL, LL, I, P, P, P, P, P, I, I, I, I, P, P],
             "moe_gate_pack": [P, P, I, I, I, I, I, P, I, P],
-            "moe_latent_prepare": [P, I, P, P, P, F, I, I, I, I, I, P, P, I, P, P, P, P, P, I, I, I, I, P, P],
+            "moe_latent_prepare": [P, I, P, P, P, F, I, I, I, I, I, P, P, I, P, P, P, P, P, I, I, I, I, P, I, P],
             "moe_heads_transpose": [P, I, LL, LL, I, I, I, I, P, I, P],
             "moe_diff_combine": [P, P, I, I, I, I, I, F, F, F, P, I, P],
             "moe_add_row": [P, P, P, LL, I, P],
@@ -349,16 +349,18 @@ def gate_pack(ctx, out, *, nh, dv, width, gate=None):
     _ok(lib().moe_gate_pack(_p(ctx), _p(gate), ld, T, nh, dv, width, _p(out), _dt(out), _stream()), "gate_pack")
 
 
-def latent_prepare(proj, batch, *, nh, d, r, width, weight, eps, q_t, k_new, commit=None, status=None):
+def latent_prepare(proj, batch, *, nh, d, r, width, weight, eps, q_t, k_new, commit=None, status=None,
+                   token_major=False):
     """From a step's 32-bit projection rows [q heads (nh x d) | latent (r)]: the latent divided by its
     root mean square, times ``weight``, into ``k_new`` [T, width] (zero-filled beyond r) and, with
     ``commit`` (a cache view), appended to that cache layer; the queries head by head into ``q_t``
-    [nh, T, d]."""
+    [nh, T, d], or with ``token_major`` token by token into ``q_t`` [T, nh, width] (zero-filled
+    beyond d)."""
     _chk(proj, "proj", torch.float32, 2), _chk(weight, "latent norm weight", torch.float32, 1)
     T = proj.shape[0]
     _chk(q_t, "q_t"), _chk(k_new, "k_new")
-    if (proj.shape[1] < nh * d + r or weight.numel() != r or q_t.numel() != nh * T * d or k_new.numel() != T * width
-            or q_t.dtype != k_new.dtype or width < r):
+    if (proj.shape[1] < nh * d + r or weight.numel() != r or q_t.numel() != nh * T * (width if token_major else d)
+            or k_new.numel() != T * width or q_t.dtype != k_new.dtype or width < r or (token_major and width < d)):
         raise KernelError("latent_prepare: shapes or dtypes")
     kc = vc = se = sl = tb = None
     ts = ring = ps = npg = 0
@@ -370,7 +372,8 @@ def latent_prepare(proj, batch, *, nh, d, r, width, weight, eps, q_t, k_new, com
         ts, ring, ps, npg = g.table.stride(0), g.ring, g.page_size, g.num_pages
     _ok(lib().moe_latent_prepare(_p(proj), proj.stride(0), _p(batch.pos), _p(batch.seq_of_token), _p(weight), float(eps),
                                  T, nh, d, r, width, _p(q_t), _p(k_new), _dt(k_new), _p(kc), _p(vc), _p(se), _p(sl),
-                                 _p(tb), ts, ring, ps, npg, _p(status), _stream()), "latent_prepare")
+                                 _p(tb), ts, ring, ps, npg, _p(status), 1 if token_major else 0, _stream()),
+        "latent_prepare")
 
 
 def heads_transpose(src, dst, *, n):

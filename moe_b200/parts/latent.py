@@ -12,15 +12,26 @@ With n the layer's normed input, H heads, d the query/key size, dv the value siz
 How it runs.  q_h . (Wuk_h c) = (Wuk_h^T q_h) . c and sum_j p_j Wuv_h c_j = Wuv_h sum_j p_j c_j, so the
 attention runs over the cached latents alone: H query heads of r numbers on ONE key/value head
 whose keys ARE its values (``KVRequest.values_are_keys``: one plane of the paged cache, r numbers a
-position whatever H is).  The two per-head products are grouped products, a group a head, through
-the kernels the routed experts use; their rows lie head by head, which ``latent_prepare`` (latent
-norm, key record, append, queries head by head) and ``heads_transpose`` arrange.  The attention
-kernels are the ones every other layer uses, with the sink's per-head number as one more parameter
-of their common variant.  Records have one width D >= r (zero-filled).
+position whatever H is).  The attention kernels are the ones every other layer uses, with the
+sink's per-head number as one more parameter of their common variant.  Records have one width
+D >= r (zero-filled).  Each of the two per-head products runs in one of two forms, chosen when the
+weights are bound by the number of weight elements a token then meets (``absorb``: "auto", or True /
+False for both sides):
+
+* folded into its neighbour: Wuk_h^T Wq_h (r x hidden a head) stands in the input projection's place,
+  so the projection's output row already holds the queries over the latent, and Wo_h Wuv_h (hidden x r
+  a head) in the output projection's, which then reads the attended latents as they come; cheaper
+  while r (hidden) <= d (hidden + r), resp. dv (hidden + r): a latent no larger than a head.  The folded
+  matrices are formed once in float64 from the checkpoint's values and rounded once to the weights'
+  dtype.  A latent layer is then norm, projection, ``latent_prepare`` (latent norm, key record,
+  append, queries as records), attention, output projection.
+* on its own: a grouped product, a group a head, through the kernels the routed experts use; the
+  groups' rows lie head by head, which ``latent_prepare`` and ``heads_transpose`` arrange.  Cheaper
+  for latents several times a head's size.
 
 32-bit in both dtypes: the latent's norm, scores, softmax and sink.  The bfloat16 path rounds the
-queries (before and after their product with Wuk), the cached latent, and the attended latent
-before its product with Wuv.
+queries over the latent, the cached latent, and the attended latent before its product (and, on its
+own, the queries before and the values after their per-head product).
 """
 from __future__ import annotations
 
@@ -50,6 +61,7 @@ class LatentAttention(Part):
         self.scale = float(p["scale"])
         self.eps = float(p["eps"])
         self.sink = bool(p.get("sink", False))
+        self.absorb = p.get("absorb", "auto")
         if not (self.nh > 0 and self.hd > 0 and self.vd > 0 and 0 < self.rank <= 256):
             raise ValueError(f"latent attention: {self.nh} heads of {self.hd} / {self.vd} on a latent of {self.rank}; "
                              "the attention kernels take latents of up to 256")
@@ -75,19 +87,50 @@ class LatentAttention(Part):
         return (f"latent attention ({self.nh} heads of {self.hd}, values of {self.vd}, one cached latent of {self.rank} "
                 f"a position{', softmax with a sink a head' if self.sink else ''}), no position encoding")
 
+    def step_elements(self, tokens):
+        W, H, r = self.hidden, self.nh, self.rank
+        fq, fo = self._folds()
+        qside = H * r * W if fq else H * self.hd * (W + r)
+        oside = H * r * W if fo else H * self.vd * (W + r)
+        return float(qside + r * W + r + oside)
+
+    def _folds(self):
+        """(fold the queries' product, fold the values' product): by weight elements a token meets."""
+        if self.absorb in (True, False):
+            return bool(self.absorb), bool(self.absorb)
+        W, r = self.hidden, self.rank
+        return r * W <= self.hd * (W + r), r * W <= self.vd * (W + r)
+
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         n, H, d, dv, r = self.names, self.nh, self.hd, self.vd, self.rank
-        ws = [tensors[n["q"]], tensors[n["down"]]]
-        dt = ws[0].dtype if ws[0].dtype == ws[1].dtype else torch.float32
-        self.w_in = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()           # [H d + r, hidden]
+        self.width = D = record_width(r, r, rt.is_bf16)
+        self.fold_q, self.fold_o = self._folds()
+        wq, wdown = tensors[n["q"]], tensors[n["down"]]
+        dt = wq.dtype if wq.dtype == wdown.dtype else torch.float32
+        uk = tensors[n["up_k"]].reshape(H, d, r)
+        uv = tensors[n["up_v"]].reshape(H, dv, r)
+        wo = tensors[n["o"]]
+        if self.fold_q:
+            # rows h r ... h r + r - 1: Wuk_h^T Wq_h, the head's queries over the latent
+            wq = torch.bmm(uk.double().transpose(1, 2), wq.double().reshape(H, d, self.hidden)).reshape(H * r, self.hidden)
+            self.w_qc = None
+        else:
+            self.w_qc = uk.transpose(1, 2).contiguous()                    # grouped [head, r, d]
+        self.w_in = torch.cat([wq.to(dt), wdown.to(dt)], dim=0).contiguous()            # [H (r | d) + r, hidden]
+        self.q_cols = r if self.fold_q else d
+        if self.fold_o:
+            # columns h D ... h D + r - 1: Wo_h Wuv_h (zero beyond r, where the attended records hold zeros)
+            ov = torch.bmm(wo.double().reshape(self.hidden, H, dv).transpose(0, 1), uv.double())     # [H, hidden, r]
+            full = torch.zeros((self.hidden, H, D), dtype=torch.float64, device=ov.device)
+            full[:, :, :r] = ov.transpose(0, 1)
+            self.wo = full.reshape(self.hidden, H * D).to(wo.dtype).contiguous()
+            self.w_cv = None
+        else:
+            self.w_cv = uv.contiguous()                                    # grouped [head, dv, r]
+            self.wo = wo.contiguous()
         self.w_norm = tensors[n["down_norm"]].to(torch.float32).contiguous()
-        # grouped weights [group = head, out, in]: queries onto the latent (Wuk_h^T), attended latent onto values
-        self.w_qc = tensors[n["up_k"]].reshape(H, d, r).transpose(1, 2).contiguous()   # [H, r, d]
-        self.w_cv = tensors[n["up_v"]].reshape(H, dv, r).contiguous()                  # [H, dv, r]
         self.sinks = tensors[n["sink"]].to(torch.float32).contiguous() if self.sink else False
-        self.wo = tensors[n["o"]].contiguous()
-        self.width = record_width(r, r, rt.is_bf16)
         self._offsets = {}
 
     def _head_offsets(self, T, device):
@@ -98,20 +141,24 @@ class LatentAttention(Part):
         return o
 
     def forward(self, rt, h, batch, cache_view, state=None):
-        T, D, H, d, dv, r = batch.num_tokens, self.width, self.nh, self.hd, self.vd, self.rank
+        T, D, H, dv, r = batch.num_tokens, self.width, self.nh, self.vd, self.rank
         dev = h.act.device
-        proj = linear(rt, h.act, self.w_in)                       # [T, H d + r] 32-bit
-        q_t = rt.empty((H, T, d))
+        proj = linear(rt, h.act, self.w_in)                       # [T, H (r | d) + r] 32-bit
         k_new = rt.empty((T, 1, D))
         # a step of one token a sequence reads its own key from the cache; whole prompts read nothing
         # from it: both may append at once.  A step that goes on from the cache appends afterwards.
         early = batch.all_decode or batch.all_fresh
-        core.latent_prepare(proj, batch, nh=H, d=d, r=r, width=D, weight=self.w_norm, eps=self.eps, q_t=q_t, k_new=k_new,
-                            commit=cache_view if early else None, status=rt.status)
-        offsets = self._head_offsets(T, dev)
-        qc = grouped_linear(rt, q_t.view(H * T, d), self.w_qc, offsets, H * T)      # [H T, r] 32-bit
+        kw = dict(nh=H, d=self.q_cols, r=r, width=D, weight=self.w_norm, eps=self.eps, k_new=k_new,
+                  commit=cache_view if early else None, status=rt.status)
         q = rt.empty((T, H, D))
-        core.heads_transpose(qc.view(H, T, r), q, n=r)
+        if self.fold_q:
+            core.latent_prepare(proj, batch, q_t=q, token_major=True, **kw)
+        else:
+            q_t = rt.empty((H, T, self.hd))
+            core.latent_prepare(proj, batch, q_t=q_t, **kw)
+            offsets = self._head_offsets(T, dev)
+            qc = grouped_linear(rt, q_t.view(H * T, self.hd), self.w_qc, offsets, H * T)      # [H T, r] 32-bit
+            core.heads_transpose(qc.view(H, T, r), q, n=r)
         ctx = rt.empty((T, H, D))
         if batch.all_decode:
             core.attention_decode(q, cache_view, batch, ctx.view(T, H * D), nh=H, window=None, scale=self.scale,
@@ -135,6 +182,9 @@ class LatentAttention(Part):
                     core.attention_generic(q, k_new, k_new, cache_view, batch, ctx, **kw)
             if not early:
                 core.kv_commit(k_new, k_new, cache_view, batch, rt.status)
+        if self.fold_o:
+            return linear(rt, ctx.view(T, H * D), self.wo)
+        offsets = self._head_offsets(T, dev)
         c_t = rt.empty((H, T, r))
         core.heads_transpose(ctx, c_t, n=r)
         ov = grouped_linear(rt, c_t.view(H * T, r), self.w_cv, offsets, H * T)      # [H T, dv] 32-bit

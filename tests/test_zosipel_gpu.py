@@ -144,6 +144,14 @@ def test_latent_norm_queries_head_by_head_and_the_transposes(bf16, H, d, r, D):
     assert D == r or float(k_new[:, 0, r:].abs().max()) == 0.0                          # zero-filled beyond the latent
     q = proj[:, :H * d].reshape(T, H, d).transpose(0, 1)
     assert (q_t.double().cpu() - q.double()).abs().max() < tol * float(q.abs().max())
+    # the queries as records of the cache's width, token by token
+    if d <= D:
+        q_rec = torch.full((T, H, D), 7.0, dtype=dt, device=DEV)
+        k_two = torch.full((T, 1, D), 7.0, dtype=dt, device=DEV)
+        core.latent_prepare(dev(proj), batch, nh=H, d=d, r=r, width=D, weight=dev(wn), eps=eps, q_t=q_rec, k_new=k_two, status=status,
+                            token_major=True)
+        assert torch.equal(k_two, k_new)
+        assert torch.equal(q_rec[:, :, :d].cpu(), q_t.transpose(0, 1).cpu()) and (D == d or float(q_rec[:, :, d:].abs().max()) == 0.0)
     # [A, B, n] -> [B, A, wider], zero-filled, from either dtype into either
     for src_dt, dst_dt in ((torch.float32, dt), (dt, torch.float32), (dt, dt)):
         src = torch.randn(H, T, r + 3, generator=g).to(src_dt)
