@@ -623,7 +623,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 4)
 attn_decode_grouped_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                            const __nv_bfloat16* __restrict__ v_cache, float* __restrict__ partial,
                            const int* __restrict__ seq_of_token, const int* __restrict__ pos,
@@ -672,10 +672,8 @@ attn_decode_grouped_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
     };
     if (tb < te) load_tile(tb, 0);
     __syncthreads();
-    uint32_t qf[HD / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ks++)
-        ldsm_x4(sQ + (lane & 15) * ROW + ks * 32 + (lane >> 4) * 16, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+    const uint32_t q_at = sQ + (lane & 15) * ROW + (lane >> 4) * 16;   // the queries stay in shared memory: the output
+                                                                       // rows take the registers (four blocks an SM)
 
     float o[HD / 8][4];
 #pragma unroll
@@ -694,17 +692,25 @@ attn_decode_grouped_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
         const uint32_t kb = sK + buf * GT_KEYS * ROW, vb = sV + buf * GT_KEYS * ROW;
         const int j0 = tile * GT_KEYS + warp * 16;       // this warp's 16 keys
         if (j0 <= p && j0 + 15 >= lo) {                   // (warp-uniform) some of them are seen
-            float sc[2][4];
+            float sc[2][4], sd[2][4];                     // two chains a tile of eight keys, summed below
 #pragma unroll
-            for (int i = 0; i < 2; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+            for (int i = 0; i < 2; i++) {
+                sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+                sd[i][0] = sd[i][1] = sd[i][2] = sd[i][3] = 0.f;
+            }
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ks++) {
-                uint32_t b0, b1, b2, b3;
+                uint32_t b0, b1, b2, b3, qf[4];
                 const int r = warp * 16 + (lane & 7) + ((lane >> 4) << 3), cb = ks * 32 + ((lane >> 3) & 1) * 16;
+                ldsm_x4(q_at + ks * 32, qf[0], qf[1], qf[2], qf[3]);
                 ldsm_x4(kb + r * ROW + cb, b0, b1, b2, b3);
-                mma_bf16(sc[0], qf[ks], b0, b1);
-                mma_bf16(sc[1], qf[ks], b2, b3);
+                mma_bf16((ks & 1) ? sd[0] : sc[0], qf, b0, b1);
+                mma_bf16((ks & 1) ? sd[1] : sc[1], qf, b2, b3);
             }
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) sc[i][e] += sd[i][e];
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int i = 0; i < 2; i++) {
