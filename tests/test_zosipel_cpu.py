@@ -39,6 +39,25 @@ def test_config_parts_and_tensor_names_fit_the_checkpoint(root, name):
         assert ls.norm1.params["offset"] == 1.0
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_configurations_drawn_at_random_are_read_and_fit_their_checkpoints(root, seed):
+    from moe_b200.config import parse_config, read_config_json
+    from moe_b200.models.decoder import expected_tensors
+    from moe_b200.weights import SafetensorsStore
+
+    name = f"drawn{seed}"
+    U.CONFIGS[name] = U.drawn_config(seed)
+    d = U.model_folder(root, name)
+    arch, typed = parse_config(read_config_json(d))
+    spec = arch.model_spec(typed)
+    store = SafetensorsStore(d)
+    store.check({n: ts.shape for n, ts in expected_tensors(spec, store).items()}, spec.ignorable)
+    assert typed.to_dict() == json.load(open(d + "/config.json"))
+    loop = U.CONFIGS[name]["loop"]
+    runs = len(typed.layers) + ((loop[1] - loop[0]) * (loop[2] - 1) if loop else 0)
+    assert len(plain.layer_order(json.load(open(d + "/config.json")))) == runs == len(spec.schedule)
+
+
 def test_a_config_written_from_the_typed_form_reads_back_the_same():
     from moe_b200.config.zosipel import ZosipelConfig
 

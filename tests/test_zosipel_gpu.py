@@ -408,6 +408,28 @@ def test_whole_prompts_of_many_lengths(root, name, dtype):
     check_schedule(d, eng, reqs, helpers.whole_schedule(reqs), tol_of(name, dtype), G.flip(dtype))
 
 
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random_whole_decoded_and_batched_in_32_bit(root, seed):
+    """Sizes, orders and constants nobody chose: each request whole, with its last 40 tokens one by one,
+    and four at a time on four slots, against the plain implementation and against each other."""
+    name = f"drawn{seed}"
+    U.CONFIGS[name] = U.drawn_config(seed)
+    d, eng = engine_of(root, name, "float32", max_slots=4)
+    V = U.CONFIGS[name]["vocab"]
+    reqs = {f"r{i}": U.tokens(V, n, 50 + i + seed) for i, n in enumerate([1, 2, 37, 131, 300, 70])}
+    tol, flip = G.tol("float32"), G.flip("float32")
+    whole = check_schedule(d, eng, reqs, helpers.whole_schedule(reqs), tol, flip)
+    cuts = [check_schedule(d, eng, reqs, helpers.tail_schedule(reqs, 40), tol, flip),
+            check_schedule(d, eng, reqs, helpers.batches_schedule(reqs, 4, lambda r: max(1, len(reqs[r]) - 36)), tol, flip)]
+    for rid, rows in whole.items():
+        scale = max(float(r.abs().max()) for r in rows.values())
+        for cut in cuts:
+            for pos, row in cut[rid].items():
+                assert float((row.double() - rows[pos].double()).abs().max()) / scale < 4 * G.tol_cut("float32"), (rid, pos)
+    assert eng.cache.ledger.slots.num_held == 0
+    _engines.pop((d, "float32", 4, None))
+
 # ----------------------------------------------------------------------------- the same tokens cut differently
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)

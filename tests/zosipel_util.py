@@ -92,6 +92,54 @@ CONFIGS = {
 }
 
 
+def drawn_config(seed):
+    """A configuration drawn at random, in the form of ``CONFIGS``' entries: two to six layers of either
+    mixer, widths of 64 to 512, maps and heads of 16 to 128 numbers (multiples of 8 only), up to five
+    query heads a kv head, latents of 8 to 256, windows of 1 to 257 positions or none, part of a map,
+    all of it or nothing rotated, one to 32 experts in one to eight groups, loops of one to four passes
+    anywhere in the stack, any of the optional parts absent."""
+    import random
+
+    rng = random.Random(seed)
+    width = rng.choice([64, 96, 128, 160, 192, 256, 320, 384, 512])
+    count = rng.randint(2, 6)
+    layers = []
+    for _ in range(count):
+        if rng.random() < 0.5:
+            kv = rng.choice([1, 1, 2, 3, 4])
+            heads = kv * rng.choice([1, 2, 3, 4, 5, 8])
+            dim = rng.choice([16, 24, 32, 40, 48, 64, 80, 96, 128])
+            vdim = rng.choice([dim, 2 * dim, dim // 2, 32, 64, 72])
+            rot = rng.choice([dim, dim // 2, dim // 4 * 2, 8, 0]) // 2 * 2
+            scaling = None
+            if rot and rng.random() < 0.7:
+                scaling = (rng.choice([2.0, 4.0, 8.0, 16.0, 40.0]), rng.choice([32, 64, 128, 512, 4096]),
+                           rng.choice([32.0, 16.0, 8.0]), rng.choice([1.0, 2.0, 0.5]))
+            m = attention(heads, kv, dim, vdim, window=rng.choice([None, 1, 2, 7, 33, 64, 65, 100, 128, 200, 257]), rot=rot,
+                          base=rng.choice([100.0, 10000.0, 250000.0, 1e6]), scaling=scaling,
+                          scale=rng.choice([None, 0.1, 0.3, 1.7 / math.sqrt(dim)]),
+                          softcap=rng.choice([None, 5.0, 30.0, 50.0]), diff=rng.choice([0.0, 0.1, 0.3, 0.8]))
+        else:
+            m = latent(rng.choice([1, 2, 3, 4, 5, 6, 7, 8, 12, 16]), rng.choice([8, 16, 24, 32, 48, 64, 96, 128]),
+                       rng.choice([8, 16, 32, 40, 64, 128]), rng.choice([8, 16, 24, 32, 48, 64, 96, 128, 160, 192, 256]),
+                       scale=rng.choice([None, 0.1, 0.25]))
+        mlp = None
+        if rng.random() < 0.8:
+            groups, per = rng.choice([1, 2, 3, 4, 8]), rng.choice([1, 2, 3, 4])
+            keep = rng.randint(1, groups)
+            grouped = rng.random() < 0.8
+            top = rng.randint(1, min(keep * per if grouped else groups * per, 8))
+            mlp = moe(groups * per, top, rng.choice([16, 24, 40, 64, 96, 136]), rng.choice([0, 16, 64, 136]),
+                      groups=(groups, keep) if grouped else None)
+        layers.append(layer(m, mlp))
+    loop = None
+    if rng.random() < 0.8:
+        a = rng.randint(0, count - 1)
+        loop = (a, rng.randint(a + 1, count), rng.choice([1, 2, 3, 4]))
+    return dict(vocab=rng.choice([50, 257, 576, 1000, 2049]), width=width, eps=rng.choice([1e-5, 1e-6, 1e-3]), loop=loop,
+                layers=layers)
+
+
 def spike_token(w, cfg, token):
     """Change drawn weights of a model whose first layer is latent attention so that every query looks
     at the key of ``token`` wherever it stands: only that token has a component along feature 0,
