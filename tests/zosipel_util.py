@@ -116,7 +116,7 @@ def drawn_config(seed):
                 scaling = (rng.choice([2.0, 4.0, 8.0, 16.0, 40.0]), rng.choice([32, 64, 128, 512, 4096]),
                            rng.choice([32.0, 16.0, 8.0]), rng.choice([1.0, 2.0, 0.5]))
             m = attention(heads, kv, dim, vdim, window=rng.choice([None, 1, 2, 7, 33, 64, 65, 100, 128, 200, 257]), rot=rot,
-                          base=rng.choice([100.0, 10000.0, 250000.0, 1e6]), scaling=scaling,
+                          base=rng.choice([100.0, 10000.0, 300000.0, 1e6]), scaling=scaling,
                           scale=rng.choice([None, 0.1, 0.3, 1.7 / math.sqrt(dim)]),
                           softcap=rng.choice([None, 5.0, 30.0, 50.0]), diff=rng.choice([0.0, 0.1, 0.3, 0.8]))
         else:
@@ -136,7 +136,7 @@ def drawn_config(seed):
     if rng.random() < 0.8:
         a = rng.randint(0, count - 1)
         loop = (a, rng.randint(a + 1, count), rng.choice([1, 2, 3, 4]))
-    return dict(vocab=rng.choice([50, 257, 576, 1000, 2049]), width=width, eps=rng.choice([1e-5, 1e-6, 1e-3]), loop=loop,
+    return dict(vocab=rng.choice([50, 257, 600, 1000, 2049]), width=width, eps=rng.choice([1e-5, 1e-6, 1e-3]), loop=loop,
                 layers=layers)
 
 
