@@ -24,7 +24,7 @@ import time
 from typing import Dict, List, Tuple
 
 USAGE = """\
-moe - generation on one B200 (Qwen2 MoE, Supevik, Fogapel, Zosipel)
+moe - generation on one B200 (Qwen2 MoE, Supevik, Fogapel, Zosipel, Divadra)
 
 USAGE
   moe run   <model> [options]        generate tokens

@@ -13,3 +13,4 @@ from .qwen2_moe import Qwen2MoeConfig  # noqa: F401  (registers the architecture
 from .supevik import SupevikConfig  # noqa: F401  (registers the architecture)
 from .fogapel import FogapelConfig  # noqa: F401  (registers the architecture)
 from .zosipel import ZosipelConfig  # noqa: F401  (registers the architecture)
+from .divadra import DivadraConfig  # noqa: F401  (registers the architecture)

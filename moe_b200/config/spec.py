@@ -41,6 +41,10 @@ class LayerSpec:
     # (parts of category "scale"; block "parallel")
     scale1: Optional[PartSpec] = None
     scale2: Optional[PartSpec] = None
+    # parts of category "inconv" that replace what the mixer / the feed-forward reads, h, by
+    # h + conv(h), a causal convolution over time with per-sequence state (block "parallel")
+    pre1: Optional[PartSpec] = None
+    pre2: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

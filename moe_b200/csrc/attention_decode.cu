@@ -280,7 +280,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 #pragma unroll
             for (int g = 0; g < GH; g++) {
                 if (g >= gh) continue;                    // uniform
-                const float x = valid ? attn_score(sc[g], scale, av.softcap) : -INFINITY;
+                const float x = valid ? attn_logit(av, kvh * group + h0 + g, sc[g], scale) : -INFINITY;
                 const float m_new = fmaxf(m[g], warp_max(x));
                 float pr = 0.f, alpha = 1.f;
                 if (m_new != -INFINITY) {                 // uniform: at least one valid key so far
@@ -326,7 +326,7 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                 for (int e = 0; e < EPC; e++) d = fmaf(kn[e], qc[g][e], d);
 #pragma unroll
                 for (int off = LPR / 2; off >= 1; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-                const float x = attn_score(d, scale, av.softcap);
+                const float x = attn_logit(av, kvh * group + h0 + g, d, scale);
                 const float m_new = fmaxf(m[g], x);
                 const float alpha = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
                 const float pr = expf(x - m_new);
@@ -485,7 +485,7 @@ attn_decode_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
 #pragma unroll
             for (int g = 0; g < GHS; g++) {
                 if (g < gh) {
-                    const float x = valid ? attn_score(sc[g], scale, av.softcap) : -INFINITY;
+                    const float x = valid ? attn_logit(av, kvh * group + h0 + g, sc[g], scale) : -INFINITY;
                     const float m_new = fmaxf(m[g], warp_max(x));
                     const float alpha = (m[g] == -INFINITY) ? 0.f : expf(m[g] - m_new);
                     pr[g] = valid ? expf(x - m_new) : 0.f;
@@ -717,7 +717,9 @@ attn_decode_grouped_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloa
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int j = j0 + i * 8 + (lane & 3) * 2 + (e & 1);
-                    const float x = (j >= lo && j <= p) ? attn_score(sc[i][e], scale, av.softcap) : -INFINITY;
+                    const float x = (j >= lo && j <= p)
+                                        ? attn_logit(av, min(kvh * group + h0 + (lane >> 2) + 8 * (e >> 1), nh - 1), sc[i][e], scale)
+                                        : -INFINITY;
                     sc[i][e] = x;
                     mx[e >> 1] = fmaxf(mx[e >> 1], x);
                 }

@@ -93,7 +93,7 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const 
                 kp = k_cache + r, vp = v_cache + r;
             }
         }
-        const float sc = valid ? attn_score(dot_row(kp, qs, hd), scale, av.softcap) : -INFINITY;
+        const float sc = valid ? attn_logit(av, h, dot_row(kp, qs, hd), scale) : -INFINITY;
         const float m_new = fmaxf(m, warp_max(sc));
         const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
         const float pr = valid ? expf(sc - m_new) : 0.f;

@@ -151,7 +151,7 @@ attn_tiled_kernel(const T* __restrict__ q, const T* __restrict__ k_new, const T*
             for (int c = 0; c < 4; c++) {
                 const int j = j0 + tx * 4 + c;
                 const bool seen = row < rows && j <= p && j >= lo;
-                s[r][c] = seen ? attn_score(s[r][c], scale, var.softcap) : -INFINITY;
+                s[r][c] = seen ? attn_logit(var, h, s[r][c], scale) : -INFINITY;
                 mx = fmaxf(mx, s[r][c]);
             }
 #pragma unroll

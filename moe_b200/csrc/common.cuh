@@ -95,9 +95,18 @@ __device__ __forceinline__ float glu_mul(int act, float param, float g, float u)
 //   chunk > 0   position p sees the keys of its own chunk only: lo = (p / chunk) * chunk (chunks are
 //               counted from position 0 of the sequence); else window > 0: lo = max(0, p + 1 - window)
 //   softcap > 0 the scaled score s becomes softcap * tanh(s / softcap)
-//   sink        the softmax has one more term that carries no value: the denominator is
-//               exp(b_h) + sum_j exp(s_j), with b_h = sink_vals[h] for query head h (a learned number
-//               per head, neither scaled nor capped) or 0 where sink_vals is null
+//   sink        how the weights are normalised:
+//               ATTN_SOFTMAX  exp(s_j) / sum_j exp(s_j)
+//               ATTN_SINK     one more term that carries no value: the denominator is
+//                             exp(b_h) + sum_j exp(s_j), with b_h = sink_vals[h] for query head h (a
+//                             learned number per head, neither scaled nor capped) or 0 where sink_vals
+//                             is null
+//               ATTN_SIGMOID  no normalisation over the keys at all: the weight of key j is
+//                             sigmoid(s_j + b_h), b_h = sink_vals[h] (0 where null).  The kernels keep
+//                             their running maximum and rescaling: the "score" they see is
+//                             log sigmoid(s_j + b_h) <= 0, so exp(score - m) is the weight over exp(m),
+//                             and the denominator at the end is exp(-m) in place of the sum.
+enum : int { ATTN_SOFTMAX = 0, ATTN_SINK = 1, ATTN_SIGMOID = 2 };
 struct AttnVariant {
     int chunk;
     float softcap;
@@ -114,10 +123,20 @@ __device__ __forceinline__ float attn_score(float dot, float scale, float softca
     const float s = dot * scale;
     return softcap > 0.f ? softcap * tanhf(s / softcap) : s;
 }
+// log(sigmoid(z)) without cancellation on either side
+__device__ __forceinline__ float log_sigmoid(float z) {
+    return z >= 0.f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+}
+// what a kernel's running softmax is fed for query head h: the (capped) scaled score, or, for
+// sigmoid weights, log sigmoid(score + b_h)
+__device__ __forceinline__ float attn_logit(const AttnVariant& av, int h, float dot, float scale) {
+    const float s = attn_score(dot, scale, av.softcap);
+    return av.sink == ATTN_SIGMOID ? log_sigmoid(s + attn_sink_value(av, h)) : s;
+}
 // the denominator of a softmax whose running maximum is m and running sum (relative to m) is l
-// (sv: the sink's own score)
+// (sv: the sink's own score); for sigmoid weights exp(-m), which undoes the shift by m
 __device__ __forceinline__ float attn_denominator(float m, float l, int sink, float sv = 0.f) {
-    return sink ? l + expf(sv - m) : l;
+    return sink == ATTN_SIGMOID ? expf(-m) : sink ? l + expf(sv - m) : l;
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }

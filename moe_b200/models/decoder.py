@@ -86,7 +86,9 @@ class DecoderModel:
         # the layer left pending added); for tests and debugging, not under a captured graph
         self.stream_tap = None
         if check:
-            store.check({n: ts.shape for n, ts in expected_tensors(spec, store).items()}, spec.ignorable)
+            exp = expected_tensors(spec, store)
+            store.check({n: ts.shape for n, ts in exp.items()}, spec.ignorable,
+                        integer=[n for n, ts in exp.items() if ts.integer])
         self._validate_schedule()
 
         def bind(part: Part, **kw):
@@ -138,11 +140,22 @@ class DecoderModel:
                 out[e.cache] = self.blocks[e.layer].mixer.kv_request()
         return out
 
-    def state_requests(self) -> Dict[int, Optional[StateRequest]]:
-        out: Dict[int, Optional[StateRequest]] = {}
+    def state_requests(self) -> Dict[object, Optional[StateRequest]]:
+        """State of fixed size per sequence, by key: a cache entry's number for its mixer,
+        ("block", number) for what the block itself carries beside its mixer (every scheduled run of a
+        layer has its own), "embedding" for the embedding."""
+        out: Dict[object, Optional[StateRequest]] = {}
         for e in self.spec.schedule:
             if e.writes_cache:
                 out[e.cache] = self.blocks[e.layer].mixer.state_request()
+            own = getattr(self.blocks[e.layer], "state_request", None)
+            if own is not None:
+                if ("block", e.cache) in out:
+                    raise ValueError(f"cache entry {e.cache} is used by two runs of blocks with state of their own")
+                out[("block", e.cache)] = own()
+        own = getattr(self.embedding, "state_request", None)
+        if own is not None:
+            out["embedding"] = own()
         return out
 
     # ---- one step ------------------------------------------------------------------
@@ -150,14 +163,22 @@ class DecoderModel:
         """Run the batch's tokens through every scheduled layer, appending to the cache;
         return float32 logits [len(want_rows), vocab], or None if no row is wanted."""
         rt = self.rt
-        x = self.embedding.forward(rt, batch.token_ids, batch.num_tokens, batch)
+        if hasattr(self.embedding, "state_request"):
+            x = self.embedding.forward(rt, batch.token_ids, batch.num_tokens, batch, state=cache.state("embedding"))
+        else:
+            x = self.embedding.forward(rt, batch.token_ids, batch.num_tokens, batch)
         pending = None
         for j in self.joins:
             j.remember(rt, x)
         for e in self.spec.schedule:
             if e.join is not None:
                 x, pending = self.joins[e.join].forward(rt, x, pending), None
-            x, pending = self.blocks[e.layer].forward(rt, x, pending, batch, cache.view(e.cache), cache.state(e.cache))
+            block = self.blocks[e.layer]
+            if hasattr(block, "state_request"):
+                x, pending = block.forward(rt, x, pending, batch, cache.view(e.cache), cache.state(e.cache),
+                                           block_state=cache.state(("block", e.cache)))
+            else:
+                x, pending = block.forward(rt, x, pending, batch, cache.view(e.cache), cache.state(e.cache))
             if self.stream_tap is not None:
                 d = pending.materialize(rt) if hasattr(pending, "materialize") else pending
                 self.stream_tap.append(x.clone() if d is None else x + d)

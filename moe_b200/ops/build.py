@@ -32,7 +32,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 # library name -> sources; what a model needs is decided by the caller
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["embed_norm.cu", "dyt.cu", "layer_scale.cu", "gemm_generic.cu", "rope_cache.cu", "attention_prepare.cu",
-             "attention_conv.cu", "attention_latent.cu", "attention_generic.cu", "attention_tiled.cu", "attention_decode.cu", "wkv.cu",
+             "attention_conv.cu", "attention_latent.cu", "attention_rotval.cu", "seq_conv.cu", "ssd.cu", "attention_generic.cu", "attention_tiled.cu", "attention_decode.cu", "wkv.cu",
              "moe.cu", "sampling.cu"],
     # tcgen05 / TMA kernels of the bfloat16 path; a float32 model never builds or loads them
     "tc": ["gemm_tc.cu", "attention_prefill.cu", "attention_prefill_tc.cu"],

@@ -72,6 +72,16 @@ def lib():
             "moe_logprobs": [P, I, I, P, I, P, P, P, P],
             "moe_seed_rng": [P, P, P, I, P],
             "moe_table_update": [P, I, P, I, P],
+            "moe_whole_prepare": [P, I, P, P, P, P, F, P, I, P, I, I, I, I, I, I, P, P, P, LL, LL, I, P, P, P, P, P, I, I, I, I,
+                                  P, P],
+            "moe_unrotate_pack": [P, P, P, I, I, I, I, P, I, P],
+            "moe_seq_conv": [I, P, LL, P, P, P, P, P, P, LL, P, P, P, P, P, I, I, LL, P, P, P, P, I, I, I, I, P],
+            "moe_embed_pair": [P, P, I, P, F, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P],
+            "moe_pair_norm_mean": [P, P, P, P, F, I, I, P, P],
+            "moe_relu2": [P, P, I, LL, P],
+            "moe_table_route": [P, I, P, P, P, P, I, I, I, I, P, P, P, P],
+            "moe_ssd_scan": [P, LL, P, LL, P, P, P, P, LL, P, P, I, I, I, I, I, P, P],
+            "moe_ssd_finish": [P, P, LL, P, F, P, I, I, I, P, I, P],
         }
         for name, argtypes in sig.items():
             fn = getattr(L, name)
@@ -462,11 +472,17 @@ def conv_heads_prepare(proj, batch, *, nh, nkv, d, dv, width, q, k, v, taps_w=No
                                      _p(status), _stream()), "conv_heads_prepare")
 
 
-def conv_state_update(proj, state, batch, *, taps, channels):
-    """state[slot] <- the last ``taps - 1`` rows of ``proj`` that each sequence of the step holds by now."""
-    _chk(proj, "proj", torch.float32, 2), _chk(state, "state", torch.float32, 2)
-    _ok(lib().moe_conv_state_update(_p(proj), proj.stride(0), _p(state), state.stride(0), int(taps), int(channels),
-                                    _p(batch.cu_seqlens), _p(batch.slots), batch.num_seqs, _stream()), "conv_state_update")
+def conv_state_update(proj, state, batch, *, taps, channels, offset=0):
+    """state[slot] <- the last ``taps - 1`` rows of ``proj`` that each sequence of the step holds by now.
+    ``proj``: float32 [T, >= channels] (a column slice is fine); the rows live from float ``offset`` on
+    in a slot's row of ``state``."""
+    _chk(state, "state", torch.float32, 2)
+    if (proj.dtype != torch.float32 or not proj.is_cuda or proj.dim() != 2 or proj.stride(1) != 1
+            or proj.shape[1] < channels or offset + (taps - 1) * channels > state.shape[1]):
+        raise KernelError("conv_state_update: the rows must be float32 [T, >= channels] and fit the state")
+    _ok(lib().moe_conv_state_update(_p(proj), proj.stride(0), state.data_ptr() + 4 * int(offset), state.stride(0),
+                                    int(taps), int(channels), _p(batch.cu_seqlens), _p(batch.slots), batch.num_seqs,
+                                    _stream()), "conv_state_update")
 
 
 WKV_FUSED_RANK = 32      # widest narrow projection of the decay that ``wkv_shift_mix`` forms itself
@@ -478,7 +494,9 @@ def wkv_shift_mix(h32, mu, state, batch, out, last32=None, decay=None):
     ``last32`` (float32 [T, width]) receives the last blend instead of ``out``; or ``decay=(w1, w2t, w0,
     out)`` (w1 [rank <= 32, width], w2t [rank, inner], w0 [inner], out float32 [T, inner]) turns it into
     exp(-exp(w0 + w2t^T tanh(w1 x))) in the same launch."""
-    _chk(h32, "h", torch.float32, 2), _chk(mu, "mu", torch.float32, 2), _chk(state, "state", torch.float32, 2)
+    _chk(h32, "h", torch.float32, 2), _chk(mu, "mu", torch.float32, 2)
+    if not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1:
+        raise KernelError("wkv_shift_mix: the state must be float32 rows (a column slice is fine)")
     T, W = h32.shape
     _chk(out, "out", dims=3)
     elsewhere = 1 if (last32 is not None or decay is not None) else 0
@@ -676,10 +694,25 @@ def kv_commit(k_new, v_new, view, batch, status):
         "kv_commit")
 
 
+class SigmoidWeights:
+    """As an attention kernel's ``sink``: the weight of a visible key is sigmoid(score + bias[h]) and the
+    weights are not normalised over the keys (``bias``: float32 [heads] or None)."""
+
+    def __init__(self, bias=None):
+        if bias is not None:
+            _chk(bias, "head bias", torch.float32, 1)
+        self.bias = bias
+
+
+ATTN_SIGMOID = 2     # AttnVariant.sink in csrc/common.cuh
+
+
 def _variant(chunk, softcap, sink):
     """(chunk, softcap, sink, the sink's values per head) as the kernels take them: see AttnVariant in
-    csrc/common.cuh.  ``sink``: False, True (a term of score 0) or a float32 tensor with one number
-    per query head (the term's own score)."""
+    csrc/common.cuh.  ``sink``: False, True (a term of score 0), a float32 tensor with one number
+    per query head (the term's own score), or ``SigmoidWeights``."""
+    if isinstance(sink, SigmoidWeights):
+        return int(chunk or 0), float(softcap or 0.0), ATTN_SIGMOID, _p(sink.bias)
     if isinstance(sink, torch.Tensor):
         _chk(sink, "sink", torch.float32, 1)
         return int(chunk or 0), float(softcap or 0.0), 1, sink.data_ptr()
@@ -1059,3 +1092,183 @@ def route_dispatch(h32, w_router, top_k, norm_topk, scale, *, shared_gate_w=None
                                  _p(sorted_token), _p(pos_of_pair), _p(gather), _p(xs), row_bytes, _p(status),
                                  _p(_router_bias(bias, E)), int(groups), int(keep), _stream()), "route_dispatch")
     return topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs
+
+
+def whole_prepare(proj, batch, *, nh, nkv, d, dv, width, q, k, v, q_norm=None, k_norm=None, eps=0.0, freq=None, rot=0,
+                  vfreq=None, commit=None, status=None):
+    """From a step's 32-bit projection rows [q heads | k heads | v heads]: an RMS norm over ALL query
+    channels at once and over all key channels (``q_norm`` [nh * d], ``k_norm`` [nkv * d]; None: no norm),
+    the rotation of the first ``rot`` dimensions of query and key heads (pairs (i, i + rot/2)), the
+    rotation of every value head over all its dimensions by the token's position (``vfreq`` [dv / 2]; None:
+    values pass), and the split into q [T, nh, width] and k, v [T, nkv, width], zero-filled.
+    ``commit=view`` also appends keys and values to that cache layer."""
+    _chk(proj, "proj", torch.float32, 2)
+    T = proj.shape[0]
+    for t, n in ((q, nh), (k, nkv), (v, nkv)):
+        if (not t.is_cuda or t.dtype != q.dtype or tuple(t.shape) != (T, n, width) or t.stride(2) != 1
+                or t.stride(1) != width or t.stride(0) < n * width):
+            raise KernelError("whole_prepare: q, k, v must be [T, heads, width] with dense heads, of one dtype")
+    if k.stride(0) != v.stride(0) or proj.shape[1] < (nh + nkv) * d + nkv * dv:
+        raise KernelError("whole_prepare: token pitch of keys and values, or projection width")
+    for w, n in ((q_norm, nh * d), (k_norm, nkv * d)):
+        if w is not None:
+            _chk(w, "norm weight", torch.float32, 1)
+            if w.numel() != n:
+                raise KernelError("whole_prepare: a norm weight has one factor per channel of the projection")
+    if rot:
+        _chk(freq, "freq", torch.float32, 1)
+        if freq.numel() < rot // 2:
+            raise KernelError("whole_prepare: frequency table too short")
+    if vfreq is not None:
+        _chk(vfreq, "vfreq", torch.float32, 1)
+        if dv % 2 or vfreq.numel() < dv // 2:
+            raise KernelError("whole_prepare: rotated values need an even width and dv / 2 frequencies")
+    kc = vc = se = sl = tb = None
+    ts = ring = ps = npg = 0
+    if commit is not None:
+        g = commit.group
+        if k.dtype != g.dtype or g.num_kv_heads != nkv or g.head_dim != width:
+            raise KernelError("whole_prepare: the cache layer differs from the keys in dtype or shape")
+        kc, vc, se, sl, tb = commit.k, commit.v, batch.seq_end, batch.slots, g.table
+        ts, ring, ps, npg = g.table.stride(0), g.ring, g.page_size, g.num_pages
+    _ok(lib().moe_whole_prepare(_p(proj), proj.stride(0), _p(batch.pos), _p(batch.seq_of_token), _p(q_norm), _p(k_norm),
+                                float(eps), _p(freq) if rot else None, int(rot), _p(vfreq), T, nh, nkv, d, dv, width,
+                                _p(q), _p(k), _p(v), q.stride(0), k.stride(0), _dt(q), _p(kc), _p(vc), _p(se), _p(sl),
+                                _p(tb), ts, ring, ps, npg, _p(status), _stream()), "whole_prepare")
+
+
+def unrotate_pack(ctx, pos, vfreq, out, *, nh, dv, width):
+    """out[t, h * dv + :] = head h of ctx [T, nh, width] turned back by the token's position: pair
+    (m, m + dv/2) by -pos * vfreq[m]; the record's columns beyond dv are dropped."""
+    _chk(ctx, "ctx", dims=3), _chk(out, "out", dims=2), _chk(vfreq, "vfreq", torch.float32, 1)
+    T = ctx.shape[0]
+    if (ctx.shape[1:] != (nh, width) or out.dtype != ctx.dtype or tuple(out.shape) != (T, nh * dv) or dv % 2
+            or vfreq.numel() < dv // 2 or width < dv):
+        raise KernelError("unrotate_pack: shapes or dtypes")
+    _ok(lib().moe_unrotate_pack(_p(ctx), _p(pos), _p(vfreq), T, nh, dv, width, _p(out), _dt(out), _stream()),
+        "unrotate_pack")
+
+
+SEQ_CONV_ACTS = {None: 0, "silu": 1}
+
+
+def seq_conv(jobs, state, batch, *, taps, channels, residual=False, act=None):
+    """A causal convolution over time on every channel, for one or two inputs of one shape in a launch.
+    ``jobs``: a list of dicts with ``u`` (float32 [T, >= channels], the step's rows; a column slice is
+    fine), ``w`` (float32 [taps, channels]), ``bias`` (float32 [channels] or None), ``offset`` (where the
+    job's (taps - 1) * channels floats start in a row of ``state``) and ``out32`` / ``out16`` ([T, channels]
+    or None).  y_t = act(sum_j w[j] u_(t - taps + 1 + j) + bias) (+ u_t with ``residual``); rows before
+    the step come from the state (the last taps - 1 rows of the sequence, oldest first).  In a step of
+    one token a sequence the state is moved on here; otherwise the caller runs ``conv_state_update``."""
+    if not 1 <= len(jobs) <= 2:
+        raise KernelError("seq_conv: one or two jobs")
+    if taps > 1:
+        _chk(state, "state", torch.float32, 2)
+    args = []
+    T = jobs[0]["u"].shape[0]
+    for j in jobs:
+        u, w = j["u"], j["w"]
+        if (u.dtype != torch.float32 or not u.is_cuda or u.dim() != 2 or u.stride(1) != 1 or u.shape[0] != T
+                or u.shape[1] < channels):
+            raise KernelError("seq_conv: the rows must be float32 [T, >= channels]")
+        _chk(w, "taps", torch.float32, 2)
+        if tuple(w.shape) != (taps, channels):
+            raise KernelError("seq_conv: a tap has one factor per channel")
+        if j.get("bias") is not None:
+            _chk(j["bias"], "bias", torch.float32, 1)
+        o32, o16 = j.get("out32"), j.get("out16")
+        for o, dt in ((o32, torch.float32), (o16, torch.bfloat16)):
+            if o is not None:
+                _chk(o, "out", dt, 2)
+                if tuple(o.shape) != (T, channels):
+                    raise KernelError("seq_conv: output shape")
+        st = None
+        if taps > 1:
+            off = int(j.get("offset", 0))
+            if off + (taps - 1) * channels > state.shape[1]:
+                raise KernelError("seq_conv: the state's row is too short")
+            st = state.data_ptr() + 4 * off
+        args += [_p(u), u.stride(0), _p(w), _p(j.get("bias")), st, _p(o32), _p(o16)]
+    if len(jobs) == 1:
+        args += [None, 0, None, None, None, None, None]
+    _ok(lib().moe_seq_conv(len(jobs), *args, int(taps), int(channels), state.stride(0) if taps > 1 else 0,
+                           _p(batch.seq_of_token), _p(batch.pos), _p(batch.cu_seqlens), _p(batch.slots), T,
+                           1 if residual else 0, SEQ_CONV_ACTS[act], 1 if (batch.all_decode and taps > 1) else 0,
+                           _stream()), "seq_conv")
+
+
+def embed_pair(table, pair, norm_w, eps, batch, out, prev_state, *, buckets, mul_prev, mul_cur, status):
+    """out = rmsnorm(table[token] + pair[(previous * mul_prev + token * mul_cur) mod buckets]) * norm_w, row
+    ``buckets`` of ``pair`` at a sequence's first position; ``prev_state`` (int32 [slots + 1]) holds the
+    token every sequence saw last and is moved on."""
+    _chk(table, "table", dims=2), _chk(pair, "pair", dims=2), _chk(norm_w, "norm weight", torch.float32, 1)
+    _chk(out, "out", torch.float32, 2), _chk(prev_state, "prev_state", torch.int32)
+    T, H = out.shape
+    if table.dtype != pair.dtype or table.shape[1] != H or pair.shape != (buckets + 1, H) or norm_w.numel() != H:
+        raise KernelError("embed_pair: shapes or dtypes")
+    _ok(lib().moe_embed_pair(_p(table), _p(pair), _dt(table), _p(norm_w), float(eps), _p(batch.token_ids), _p(out), T, H,
+                             table.shape[0], int(buckets), int(mul_prev), int(mul_cur), _p(prev_state),
+                             _p(batch.seq_of_token), _p(batch.pos), _p(batch.cu_seqlens), _p(batch.slots),
+                             _p(getattr(batch, "last_token", None)), _p(status), _stream()), "embed_pair")
+
+
+def pair_norm_mean(a, wa, b, wb, eps, out):
+    """out = (rmsnorm(a) * wa + rmsnorm(b) * wb) / 2 over the last axis, 32-bit."""
+    for t in (a, b, out):
+        _chk(t, "rows", torch.float32, 2)
+    _chk(wa, "wa", torch.float32, 1), _chk(wb, "wb", torch.float32, 1)
+    T, H = a.shape
+    if b.shape != a.shape or out.shape != a.shape or wa.numel() != H or wb.numel() != H:
+        raise KernelError("pair_norm_mean: shapes")
+    _ok(lib().moe_pair_norm_mean(_p(a), _p(wa), _p(b), _p(wb), float(eps), T, H, _p(out), _stream()), "pair_norm_mean")
+
+
+def relu2(x, out):
+    """out = relu(x)^2, rounded to ``out``'s dtype."""
+    _chk(x, "x", torch.float32), _chk(out, "out")
+    if out.numel() != x.numel():
+        raise KernelError("relu2: sizes differ")
+    _ok(lib().moe_relu2(_p(x), _p(out), _dt(out), x.numel(), _stream()), "relu2")
+
+
+def table_route(table, batch, top_k, num_experts, topk_idx, topk_w, status):
+    """topk_idx[t, :] = table[token id of row t, :top_k]; every weight 1 / top_k; rows of no sequence get
+    no expert."""
+    _chk(table, "table", torch.int32, 2), _chk(topk_idx, "topk_idx", torch.int32, 2)
+    _chk(topk_w, "topk_w", torch.float32, 2)
+    T = topk_idx.shape[0]
+    if table.shape[1] < top_k or tuple(topk_idx.shape) != (T, top_k) or tuple(topk_w.shape) != (T, top_k):
+        raise KernelError("table_route: shapes")
+    _ok(lib().moe_table_route(_p(table), table.shape[1], _p(batch.token_ids), _p(batch.seq_of_token), _p(batch.slots),
+                              _p(getattr(batch, "last_token", None)), T, table.shape[0], int(top_k), int(num_experts),
+                              _p(topk_idx), _p(topk_w), _p(status), _stream()), "table_route")
+
+
+def ssd_scan(xbc, dt_raw, dt_bias, a_log, dskip, state, batch, y, *, heads, groups, n, dv, offset=0):
+    """Per sequence and head, tokens in order: dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S +
+    dt B x^T, y = S^T C + dskip x.  ``xbc``: float32 [T, heads * dv + 2 groups n] = [x | B | C]; ``dt_raw``:
+    float32 [T, heads] (a column slice is fine); ``state``: float32 [slots + 1, ...] whose rows hold
+    heads * n * dv floats from ``offset``; y: float32 [T, heads * dv]."""
+    _chk(xbc, "xbc", torch.float32, 2), _chk(y, "y", torch.float32, 2)
+    for t in (dt_bias, a_log, dskip):
+        _chk(t, "per-head constant", torch.float32, 1)
+    T = y.shape[0]
+    if (dt_raw.dtype != torch.float32 or dt_raw.dim() != 2 or dt_raw.stride(1) != 1 or tuple(dt_raw.shape) != (T, heads)
+            or xbc.shape != (T, heads * dv + 2 * groups * n) or y.shape[1] != heads * dv or state.dtype != torch.float32
+            or state.stride(1) != 1 or offset + heads * n * dv > state.shape[1] or dt_bias.numel() != heads):
+        raise KernelError("ssd_scan: shapes")
+    _ok(lib().moe_ssd_scan(_p(xbc), xbc.stride(0), _p(dt_raw), dt_raw.stride(0), _p(dt_bias), _p(a_log), _p(dskip),
+                           state.data_ptr() + 4 * offset, state.stride(0), _p(batch.cu_seqlens), _p(batch.slots),
+                           batch.num_seqs, heads, groups, n, dv, _p(y), _stream()), "ssd_scan")
+
+
+def ssd_finish(y, z, norm_w, eps, batch, out, *, norm_groups):
+    """out = norm(y * silu(z)): an RMS norm over each of ``norm_groups`` equal parts of the row, times
+    ``norm_w``, rounded to ``out``'s dtype.  ``z``: float32 [T, inner], a column slice is fine."""
+    _chk(y, "y", torch.float32, 2), _chk(norm_w, "norm weight", torch.float32, 1), _chk(out, "out", dims=2)
+    T, inner = y.shape
+    if (z.dtype != torch.float32 or z.stride(1) != 1 or tuple(z.shape) != (T, inner) or out.shape != y.shape
+            or norm_w.numel() != inner or inner % norm_groups):
+        raise KernelError("ssd_finish: shapes")
+    _ok(lib().moe_ssd_finish(_p(y), _p(z), z.stride(0), _p(norm_w), float(eps), _p(batch.seq_of_token), T, inner,
+                             int(norm_groups), _p(out), _dt(out), _stream()), "ssd_finish")

@@ -37,6 +37,17 @@ A second prepared path, whose kernel ``conv_heads_prepare`` stands in the same p
   unit_norm   {"eps": e}: after the rotation, query and key heads are divided by their root mean
               square (no weight);
   a rotation of pairs (2i, 2i + 1) (position option ``interleaved``).
+
+A third prepared path, whose kernel ``whole_prepare`` stands in the same place, is taken by
+  qk_norm     {"eps": e, "whole": True}: ONE root mean square over all query channels of a token (and
+              one over all key channels) before the split into heads, with a weight per channel
+              (tensors of the projections' sizes);
+  rotate_values  the value of position j is rotated by j over all of its dv dimensions, pair
+              (m, m + dv/2) by j * theta^(-2m/dv) (theta: the position encoding's), and cached so; a
+              head's output at position i is turned back by -i, so that every value arrives turned
+              by its distance to the query;
+  sigmoid     the weight of a visible key is sigmoid(score + b_h), b_h a learned number per head
+              (tensor role ``head_bias``), and the weights are not normalised over the keys.
 """
 from __future__ import annotations
 
@@ -68,7 +79,7 @@ class GQAttention(Part):
                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "gate": "gate_proj.weight",
                      "o_bias": "o_proj.bias", "q_conv": "q_conv.weight", "k_conv": "k_conv.weight",
-                     "v_conv": "v_conv.weight"}
+                     "v_conv": "v_conv.weight", "head_bias": "head_bias"}
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -90,6 +101,10 @@ class GQAttention(Part):
         self.o_bias = bool(p.get("o_bias", False))
         self.taps = int((p.get("conv") or {}).get("taps", 0) or 0)
         self.unit_norm = p.get("unit_norm")
+        self.whole_norm = bool((self.qk_norm or {}).get("whole", False))
+        self.rotate_values = bool(p.get("rotate_values", False))
+        self.sigmoid = bool(p.get("sigmoid", False))
+        self.whole_path = self.whole_norm or self.rotate_values or self.sigmoid
         pos = dict(p.get("position") or {"kind": "none"})
         self.position = make_part("position", PartSpec(pos.pop("kind"), pos, spec.prefix))
         # the prepared path: a kernel of its own between projection and attention, records of width D
@@ -99,6 +114,18 @@ class GQAttention(Part):
         self.conv_path = bool(self.taps or self.unit_norm or getattr(self.position, "interleaved", False))
         self.variant = dict(chunk=self.chunk, softcap=self.softcap, sink=self.sink)
         self.plain_scores = not (self.chunk or self.softcap or self.sink)    # what the fused decode kernel computes
+        if self.whole_path:
+            if (self.conv_path or self.out_gate or self.bias or self.sink or not self.own_kv or self.cos_sin_scale != 1.0
+                    or (self.qk_norm and not self.whole_norm)):
+                raise ValueError("whole-projection norm, rotated values and sigmoid weights go with none of: convolution, "
+                                 "unit norm, pairs (2i, 2i + 1), output gate, biases, sink, another layer's cache, "
+                                 "scaled cos and sin, a per-head q/k norm")
+            if self.rotate_values and self.vd % 2:
+                raise ValueError("rotated values need an even value size")
+            if not (0 < self.hd <= 256 and 0 < self.vd <= 256):
+                raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels take up to 256")
+            self.prepared = False
+            self.plain_scores = False
         if self.nh % self.nkv:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if self.chunk < 0 or self.softcap < 0 or self.taps < 0 or self.taps > 16:
@@ -111,14 +138,14 @@ class GQAttention(Part):
             if not (0 < self.hd <= 256 and 0 < self.vd <= 256):
                 raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels take up to 256")
             self.prepared = False
-        elif (self.chunk or self.softcap or self.sink) and not self.prepared:
+        elif (self.chunk or self.softcap or self.sink) and not self.prepared and not self.whole_path:
             self.prepared = True          # the path whose every step takes the kernels with these options
         if self.prepared:
             if not self.own_kv:
                 raise ValueError("a layer that reads another layer's cache takes none of value_dim, qk_norm, out_gate")
             if not (0 < self.hd <= 256 and 0 < self.vd <= 256):
                 raise ValueError(f"head sizes {self.hd} / {self.vd}: the attention kernels take up to 256")
-        elif not self.conv_path and (self.hd % 16 or not 16 <= self.hd <= 256):
+        elif not self.conv_path and not self.whole_path and (self.hd % 16 or not 16 <= self.hd <= 256):
             raise ValueError(f"head_dim {self.hd}: the attention kernels take multiples of 16 from 16 to 256")
         if self.window is not None and self.window <= 0:
             raise ValueError("window must be positive")
@@ -139,8 +166,10 @@ class GQAttention(Part):
                 t[n["k_bias"]] = TensorSpec((self.nkv * self.hd,), vector=True)
                 t[n["v_bias"]] = TensorSpec((self.nkv * self.vd,), vector=True)
         if self.qk_norm:
-            t[n["q_norm"]] = TensorSpec((self.hd,), init="ones", vector=True)
-            t[n["k_norm"]] = TensorSpec((self.hd,), init="ones", vector=True)
+            t[n["q_norm"]] = TensorSpec((self.nh * self.hd if self.whole_norm else self.hd,), init="ones", vector=True)
+            t[n["k_norm"]] = TensorSpec((self.nkv * self.hd if self.whole_norm else self.hd,), init="ones", vector=True)
+        if self.sigmoid:
+            t[n["head_bias"]] = TensorSpec((self.nh,), init="zeros", vector=True)
         if self.out_gate:
             t[n["gate"]] = TensorSpec((self.nh * self.vd, self.hidden))
         if self.o_bias:
@@ -165,7 +194,11 @@ class GQAttention(Part):
         if self.vd != self.hd:
             d += f", value heads of {self.vd}"
         if self.qk_norm:
-            d += ", q/k RMS norm"
+            d += ", q/k RMS norm" + (" over the whole projection" if self.whole_norm else "")
+        if self.rotate_values:
+            d += ", values rotated by their distance"
+        if self.sigmoid:
+            d += ", sigmoid weights with a bias a head"
         if self.out_gate:
             d += ", sigmoid output gate"
         if self.taps:
@@ -222,8 +255,15 @@ class GQAttention(Part):
         self.position.bind(tensors, rt)
         self.scale = (float(self.fixed_scale) if self.fixed_scale is not None
                       else self.position.attention_scale() / math.sqrt(self.hd))
-        if self.prepared or self.conv_path:
+        if self.prepared or self.conv_path or self.whole_path:
             self.width = record_width(self.hd, self.vd, rt.is_bf16)
+        self.vfreq = None
+        if self.rotate_values:
+            from .rope import rotary_inv_freq
+
+            self.vfreq = rotary_inv_freq(float(getattr(self.position, "theta", 10000.0)), self.vd).to(rt.device)
+        if self.sigmoid:
+            self.variant = dict(self.variant, sink=core.SigmoidWeights(tensors[n["head_bias"]].to(torch.float32).contiguous()))
         # Single-token steps append in heads_prepare and attend with the split kernel, whose merge gates
         # and packs (three launches).  MOE_B200_PREPARED_FUSED=1 takes the fused decode kernel instead
         # (two launches); measured slower on a B200 at widths of 2,048 and 4,096 (0.61 against 0.55 ms a
@@ -288,10 +328,32 @@ class GQAttention(Part):
             core.conv_state_update(proj, state, batch, taps=self.taps, channels=self.channels)
         return self._attend_prepared(rt, batch, cache_view, q, k_new, v_new, ctx, None, early)
 
+    def _forward_whole(self, rt, h, batch, cache_view):
+        """Projection -> norm over the whole of q and of k, rotation of q and k, rotation of the values,
+        split and append -> attention over records of width D -> the output turned back and packed ->
+        output projection."""
+        T, D, nh, nkv = batch.num_tokens, self.width, self.nh, self.nkv
+        proj = linear(rt, h.act, self.wqkv)
+        table, rot = self.position.rotary_table()
+        q = rt.empty((T, nh, D))
+        k_new, v_new = rt.empty((T, nkv, D)), rt.empty((T, nkv, D))
+        ctx = rt.empty((T, nh, D))
+        if getattr(batch, "has_padding", False) and not batch.all_decode:
+            ctx.zero_()
+        early = batch.all_decode or batch.all_fresh
+        core.whole_prepare(proj, batch, nh=nh, nkv=nkv, d=self.hd, dv=self.vd, width=D, q=q, k=k_new, v=v_new,
+                           q_norm=self.q_norm_w, k_norm=self.k_norm_w, eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0,
+                           freq=table, rot=rot, vfreq=self.vfreq, commit=cache_view if early else None, status=rt.status)
+        return self._attend_prepared(rt, batch, cache_view, q, k_new, v_new, ctx, None, early)
+
     def _attend_prepared(self, rt, batch, cache_view, q, k_new, v_new, ctx, gate, early):
         """Attention over prepared records of width D, packing (and gate), output projection."""
         T, D, nh, nkv = batch.num_tokens, self.width, self.nh, self.nkv
-        if batch.all_decode:
+        if batch.all_decode and self.rotate_values:
+            # (the merge of the splits leaves whole records; the turn back packs them)
+            core.attention_decode(q, cache_view, batch, ctx, nh=nh, window=self.window, scale=self.scale,
+                                  status=rt.status, **self.variant)
+        elif batch.all_decode:
             # (the merge of the splits multiplies by the gate and packs the heads)
             packed = rt.empty((T, nh * self.vd))
             core.attention_decode(q, cache_view, batch, packed, nh=nh, window=self.window, scale=self.scale,
@@ -299,7 +361,7 @@ class GQAttention(Part):
             return linear(rt, packed, self.wo, bias=self.bo)
         else:
             done = False
-            if rt.is_bf16:
+            if rt.is_bf16 and not self.sigmoid:
                 from ..ops import tc
 
                 if batch.all_fresh:
@@ -314,7 +376,10 @@ class GQAttention(Part):
                     core.attention_generic(q, k_new, v_new, cache_view, batch, ctx, **kw)
             if not early:
                 core.kv_commit(k_new, v_new, cache_view, batch, rt.status)
-        if self.out_gate or D != self.vd:
+        if self.rotate_values:
+            packed = rt.empty((T, nh * self.vd))
+            core.unrotate_pack(ctx, batch.pos, self.vfreq, packed, nh=nh, dv=self.vd, width=D)
+        elif self.out_gate or D != self.vd:
             packed = rt.empty((T, nh * self.vd))
             core.gate_pack(ctx, packed, nh=nh, dv=self.vd, width=D, gate=gate)
         else:
@@ -324,6 +389,8 @@ class GQAttention(Part):
     def forward(self, rt, h, batch, cache_view, state=None):
         if self.conv_path:
             return self._forward_conv(rt, h, batch, cache_view, state)
+        if self.whole_path:
+            return self._forward_whole(rt, h, batch, cache_view)
         if self.prepared:
             return self._forward_prepared(rt, h, batch, cache_view)
         T = batch.num_tokens

@@ -87,6 +87,7 @@ class TensorSpec:
     init: str = "normal"        # "normal" | "ones" | "zeros" for the random-weights mode
     vector: bool = False        # small vectors are widened to float32 when bound (exact)
     sparse: bool = False        # read only for the tokens that are routed to it (an expert's weights)
+    integer: int = 0            # > 0: a table of integers in [0, integer), the entries of a row distinct (int32)
 
 
 class Runtime:

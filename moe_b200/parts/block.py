@@ -16,7 +16,11 @@ before a sublayer may form post-norm, residual sum and its own norm in one kerne
 may be multiplied by a per-channel factor first, and the feed-forward is optional:
     n = norm1(x);  x += scale1 * mixer(n) + scale2 * ffn(n)
 The two outputs are handed on unscaled and unsummed (``ScaledPairDelta``): the next norm forms the
-scaling, the sums and itself in one kernel.
+scaling, the sums and itself in one kernel.  With ``norm2`` the feed-forward reads a norm of its own of
+the SAME x: x += mixer(norm1(x)) + ffn(norm2(x)).  With ``pre1`` / ``pre2`` (parts of category
+"inconv") what a sublayer reads, h, is first replaced by h + conv(h), a causal convolution over time
+on each channel; the last taps - 1 inputs of every sequence are state of the block, which the cache
+keeps per scheduled run of the layer (``state_request``, handed to ``forward`` as ``block_state``).
 """
 from __future__ import annotations
 
@@ -95,20 +99,31 @@ class ParallelBlock:
     category, kind = "block", "parallel"
 
     def __init__(self, layer: LayerSpec):
-        if layer.norm2 is not None or layer.post1 is not None or layer.post2 is not None:
-            raise ValueError("a parallel block has one norm, before both sublayers")
-        if layer.ffn is None and layer.scale2 is not None:
-            raise ValueError("a parallel block without a feed-forward has no factor for it")
+        if layer.post1 is not None or layer.post2 is not None:
+            raise ValueError("a parallel block has its norms before the sublayers")
+        if layer.ffn is None and (layer.scale2 is not None or layer.norm2 is not None or layer.pre2 is not None):
+            raise ValueError("a parallel block without a feed-forward has no factor, norm or convolution for it")
         self.layer = layer
         self.norm1 = make_part("norm", layer.norm1)
         self.mixer = make_part("mixer", layer.mixer)
         self.ffn = make_part("ffn", layer.ffn) if layer.ffn is not None else None
+        self.norm2 = make_part("norm", layer.norm2) if layer.norm2 is not None else None
         self.scale1 = make_part("scale", layer.scale1) if layer.scale1 is not None else None
         self.scale2 = make_part("scale", layer.scale2) if layer.scale2 is not None else None
+        self.pre1 = make_part("inconv", layer.pre1) if layer.pre1 is not None else None
+        self.pre2 = make_part("inconv", layer.pre2) if layer.pre2 is not None else None
         self._ones = None
 
     def parts(self):
-        return [p for p in (self.norm1, self.mixer, self.ffn, self.scale1, self.scale2) if p is not None]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.scale1, self.scale2, self.pre1, self.pre2)
+                if p is not None]
+
+    def state_request(self):
+        """What the input convolutions keep per sequence: [pre1's rows | pre2's rows], 32-bit."""
+        from ..cache.kv import StateRequest
+
+        n = sum(p.state_floats() for p in (self.pre1, self.pre2) if p is not None)
+        return StateRequest((n,), torch.float32) if n else None
 
     def _factor(self, rt, scale, like):
         if scale is not None:
@@ -117,14 +132,26 @@ class ParallelBlock:
             self._ones = torch.ones(like.shape[1], dtype=torch.float32, device=like.device)
         return self._ones
 
-    def forward(self, rt, x, pending, batch, cache_view, state):
-        want32 = getattr(self.mixer, "wants32", False) or getattr(self.ffn, "wants32", False)
-        h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt), want32=want32)
+    def forward(self, rt, x, pending, batch, cache_view, state, block_state=None):
+        from .conv import run_input_convs
+
+        mix32 = getattr(self.mixer, "wants32", False)
+        ffn32 = getattr(self.ffn, "wants32", False)
+        convs = self.pre1 is not None or self.pre2 is not None
+        h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt),
+                               want32=mix32 or (ffn32 and self.norm2 is None) or convs)
+        # (norm1 has written the sum back: a second norm reads the same x, with nothing pending)
+        h2 = self.norm2.forward(rt, x, want32=ffn32 or convs) if self.norm2 is not None else h
+        if convs:
+            if self.norm2 is None and self.ffn is not None and (self.pre1 is None) != (self.pre2 is None):
+                raise ValueError("a parallel block with one norm convolves both sublayers' input or neither")
+            h, h2 = run_input_convs(rt, [(self.pre1, h, mix32), (self.pre2, h2, ffn32) if self.ffn is not None else None],
+                                    batch, block_state)
         a = self.mixer.forward(rt, h, batch, cache_view, state)
         if self.ffn is None:
             return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a))
         # (a feed-forward may hand its output on uncombined, for the next norm to finish: base.LazyDelta)
-        b = getattr(self.ffn, "forward_lazy", self.ffn.forward)(rt, h, batch)
+        b = getattr(self.ffn, "forward_lazy", self.ffn.forward)(rt, h2, batch)
         return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a), b, self._factor(rt, self.scale2, a))
 
 

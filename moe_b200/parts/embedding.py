@@ -49,6 +49,52 @@ class TokenEmbedding(Part):
         return x
 
 
+class PairEmbedding(TokenEmbedding):
+    """x = rmsnorm(embed[token] + pair[row]) * w: beside the token's own row, a row of a second table
+    chosen by the token and the one before it, row = (previous * mul_prev + token * mul_cur) mod
+    buckets; a sequence's first token takes row number ``buckets`` (the table's last).  The norm's
+    statistics are 32-bit.  The token a sequence saw last is state of fixed size (``state_request``),
+    handed to ``forward`` as ``state``."""
+
+    kind = "pair_embedding"
+    default_names = {"weight": "weight", "pair": "pair", "norm": "norm"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.buckets, self.mul_prev, self.mul_cur = int(p["buckets"]), int(p["mul_prev"]), int(p["mul_cur"])
+        self.eps = float(p["eps"])
+        if self.buckets < 1 or self.scale != 1.0:
+            raise ValueError("pair_embedding: at least one bucket, and no scale")
+
+    def tensors(self):
+        n = self.names
+        return {n["weight"]: TensorSpec((self.vocab, self.hidden)), n["pair"]: TensorSpec((self.buckets + 1, self.hidden)),
+                n["norm"]: TensorSpec((self.hidden,), init="ones", vector=True)}
+
+    def describe(self):
+        return f"token embedding + a row by (previous, token) of {self.buckets} buckets, RMS-normed"
+
+    def step_elements(self, num_tokens):
+        return float(2 * num_tokens * self.hidden + self.hidden)
+
+    def state_request(self):
+        from ..cache.kv import StateRequest
+
+        return StateRequest((1,), torch.int32)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.pair = tensors[self.names["pair"]].to(self.weight.dtype).contiguous()
+        self.norm_w = tensors[self.names["norm"]].to(torch.float32).contiguous()
+
+    def forward(self, rt, token_ids, num_tokens, batch=None, state=None):
+        x = rt.empty((num_tokens, self.hidden), torch.float32)
+        core.embed_pair(self.weight, self.pair, self.norm_w, self.eps, batch, x, state, buckets=self.buckets,
+                        mul_prev=self.mul_prev, mul_cur=self.mul_cur, status=rt.status)
+        return x
+
+
 class LMHead(Part):
     category, kind = "head", "lm_head"
     graph_safe = True
@@ -170,4 +216,5 @@ class AddRowJoin(Part):
 register_part("join", "concat_linear", ConcatLinearJoin)
 register_part("join", "add_row", AddRowJoin)
 register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("embedding", "pair_embedding", PairEmbedding)
 register_part("head", "lm_head", LMHead)

@@ -66,6 +66,42 @@ class DenseSwiGLU(Part):
         return linear(rt, swiglu_linear(rt, h.act, self.w_gu, self.activation, self.limit), self.w_down)
 
 
+class DenseMLP(Part):
+    """y = Wd f(Wu n), no gate; ``activation`` names f: "relu2" is relu(z)^2.  The activation is 32-bit
+    arithmetic on the first product's 32-bit output; the bfloat16 path rounds its result."""
+
+    category, kind = "ffn", "dense_mlp"
+    graph_safe = True
+    wants32 = False
+    default_names = {"up": "up_proj.weight", "down": "down_proj.weight"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(self.params["hidden_size"])
+        self.size = int(self.params["size"])
+        self.activation = str(self.params.get("activation", "relu2"))
+        if self.activation != "relu2":
+            raise ValueError(f"dense feed-forward: activation '{self.activation}' is none of ['relu2']")
+
+    def tensors(self):
+        n = self.names
+        return {n["up"]: TensorSpec((self.size, self.hidden)), n["down"]: TensorSpec((self.hidden, self.size))}
+
+    def describe(self):
+        return f"dense {self.activation} {self.size}"
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w_up = tensors[self.names["up"]].contiguous()
+        self.w_down = tensors[self.names["down"]].contiguous()
+
+    def forward(self, rt, h, batch):
+        z = linear(rt, h.act, self.w_up)
+        act = rt.empty(z.shape)
+        core.relu2(z, act)
+        return linear(rt, act, self.w_down)
+
+
 class CombineDelta(LazyDelta):
     """The routed experts' outputs before the combine: delta[t] = sum_j w[t, j] * y[pos[t, j]] +
     gate[t] * shared[t].  An RMS norm forms it inside its own kernel."""
@@ -92,7 +128,8 @@ class RoutedExperts(Part):
                      "expert_gate": "experts.{e}.gate_proj.weight", "expert_up": "experts.{e}.up_proj.weight",
                      "expert_down": "experts.{e}.down_proj.weight",
                      "shared_gate_proj": "shared_expert.gate_proj.weight", "shared_up": "shared_expert.up_proj.weight",
-                     "shared_down": "shared_expert.down_proj.weight", "shared_gate": "shared_expert_gate.weight"}
+                     "shared_down": "shared_expert.down_proj.weight", "shared_gate": "shared_expert_gate.weight",
+                     "table": "table"}
 
     def __init__(self, spec):
         super().__init__(spec)
@@ -106,6 +143,14 @@ class RoutedExperts(Part):
         self.shared_size = int(p.get("shared_size", 0) or 0)
         self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_size > 0
         self.router_bias = bool(p.get("router_bias", False))     # logits = Wr n + b
+        # "table": no router at all; an integer table [vocab, top_k] names each token id's experts, every
+        # one with weight 1 / top_k
+        self.table = str(p.get("router", "softmax")) == "table"
+        self.vocab = int(p.get("vocab_size", 0) or 0)
+        if self.table and (self.vocab <= 0 or p.get("groups") or self.router_bias or p.get("shared_gate")):
+            raise ValueError("routing by a table needs the vocabulary's size and takes no router options")
+        if self.table:
+            self.wants32 = False
         # {"count": g, "keep": m}: the experts form g equal groups of neighbours, a group's score is its
         # best expert's, and only experts of the m best groups may be picked
         grp = p.get("groups") or {}
@@ -137,7 +182,8 @@ class RoutedExperts(Part):
         return self.names[role].format(e=e)
 
     def tensors(self):
-        t = {self.names["router"]: TensorSpec((self.E, self.hidden))}
+        t = ({self.names["table"]: TensorSpec((self.vocab, self.k), integer=self.E)} if self.table
+             else {self.names["router"]: TensorSpec((self.E, self.hidden))})
         for e in range(self.E):
             t[self._expert("expert_gate", e)] = TensorSpec((self.size, self.hidden), sparse=True)
             t[self._expert("expert_up", e)] = TensorSpec((self.size, self.hidden), sparse=True)
@@ -163,6 +209,8 @@ class RoutedExperts(Part):
         dimensions; else one tensor per expert and projection."""
         E, n, H = self.E, self.size, self.hidden
         router = self.names["router"]
+        if self.table:
+            return self.tensors()
         if has("experts.gate_up_proj"):
             t = {router: TensorSpec((E, H)), "experts.gate_up_proj": TensorSpec((E, 2 * n, H), sparse=True),
                  "experts.down_proj": TensorSpec((E, H, n), sparse=True)}
@@ -175,7 +223,8 @@ class RoutedExperts(Part):
         return self.tensors()
 
     def describe(self):
-        return (f"{self.E} experts of {self.size}, top-{self.k}, softmax gate"
+        return (f"{self.E} experts of {self.size}, top-{self.k}, "
+                + ("named by a table over token ids, equal weights" if self.table else "softmax gate")
                 + (" with bias" if self.router_bias else "")
                 + (f", within the best {self.keep} of {self.groups} groups" if self.groups else "")
                 + (", renormalised" if self.norm_topk else "")
@@ -201,9 +250,15 @@ class RoutedExperts(Part):
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         n = self.names
-        self.w_router = tensors[n["router"]].contiguous()
+        self.route_table = None
+        if self.table:
+            self.route_table = tensors[n["table"]].to(torch.int32).contiguous()
+            self.w_router = None
+            dev = self.route_table.device
+        else:
+            self.w_router = tensors[n["router"]].contiguous()
+            dev = self.w_router.device
         self.b_router = tensors[n["router_bias"]].to(torch.float32).contiguous() if self.router_bias else None
-        dev = self.w_router.device
         # The device layout is [E, 2 * size, hidden] (rows [0, size) gate, [size, 2 size) up) and
         # [E, hidden, size], whatever the checkpoint's; tensors are fetched one at a time.
         if "experts.gate_up_proj" in tensors:
@@ -238,7 +293,7 @@ class RoutedExperts(Part):
         # For prompts the router's logits come from the tensor cores: the 32-bit activations as three
         # bfloat16 terms against the (bfloat16, hence exact) router rows, three times side by side.
         self.w_router3 = None
-        if rt.is_bf16 and self.w_router.dtype == torch.bfloat16 and self.hidden % 8 == 0:
+        if rt.is_bf16 and self.w_router is not None and self.w_router.dtype == torch.bfloat16 and self.hidden % 8 == 0:
             rows = [self.w_router] + ([self.w_sgate.reshape(1, -1)] if self.w_sgate is not None else [])
             one = torch.cat(rows, dim=0)
             self.w_router3 = torch.cat([one, one, one], dim=1).contiguous()
@@ -247,9 +302,14 @@ class RoutedExperts(Part):
         """-> (topk_idx [T, k] int32, topk_w [T, k] float32, shared_gate [T] float32 or None)
         ``after_logits``: called once the logits' product is launched (or, where logits and picks are one
         launch, after that)."""
-        T = h.f32.shape[0]
+        T = h.act.shape[0]
         topk_idx = rt.empty((T, self.k), torch.int32)
         topk_w = rt.empty((T, self.k), torch.float32)
+        if self.table:
+            core.table_route(self.route_table, batch, self.k, self.E, topk_idx, topk_w, rt.status)
+            if after_logits is not None:
+                after_logits()
+            return topk_idx, topk_w, None
         sg = rt.empty((T,), torch.float32) if self.w_sgate is not None else None
         if self.w_router3 is not None and T >= self.tc_router_tokens:
             from ..ops import tc
@@ -284,7 +344,7 @@ class RoutedExperts(Part):
         tokens, norm, router and dispatch are one launch.  None if the sizes or the kind of norm do
         not allow it (the block then runs the norm itself and calls ``forward``)."""
         rms = getattr(norm, "rms_params", None)          # the norm says whether it can be run by a neighbour
-        if rms is None or x.shape[0] > self.fused_norm_tokens or self.E > 256 or self.b_router is not None:
+        if rms is None or x.shape[0] > self.fused_norm_tokens or self.E > 256 or self.b_router is not None or self.table:
             return None
         norm_w, norm_eps = rms()
         routed = core.norm_route(x, delta, norm_w, norm_eps, self.w_router, self.k, self.norm_topk, self.scale,
@@ -311,7 +371,7 @@ class RoutedExperts(Part):
                 ys = self._shared(rt, h)
         if routed is not None:
             topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = routed
-        elif few and T <= self.route_dispatch_tokens:
+        elif few and T <= self.route_dispatch_tokens and not self.table:
             # pick, table inversion and gather in one launch after the logits
             topk_idx, topk_w, sg, offsets, sorted_token, pos_of_pair, xs = core.route_dispatch(
                 h.f32, self.w_router, self.k, self.norm_topk, self.scale, shared_gate_w=self.w_sgate,
@@ -353,4 +413,5 @@ class RoutedExperts(Part):
 
 
 register_part("ffn", "dense_swiglu", DenseSwiGLU)
+register_part("ffn", "dense_mlp", DenseMLP)
 register_part("ffn", "routed_experts", RoutedExperts)

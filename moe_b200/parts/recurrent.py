@@ -156,3 +156,214 @@ class WKVMixer(Part):
 
 
 register_part("mixer", "wkv", WKVMixer)
+
+
+class SSDMixer(Part):
+    """A state-space mixer with one decay number per head and step (Mamba-2).
+
+    With n_t the layer's input, inner = heads * dv, N the state size and G groups of heads that share
+    B and C, the input projection's rows are [z: inner | x: inner | B: G N | C: G N | dt: heads].
+    x, B and C together pass a causal convolution over time per channel (taps [channels, taps] with a
+    bias; the last column multiplies the token's own row) and silu.  Per head h of group
+    g = h // (heads / G), with dt = softplus(dt + dt_bias_h) and a state S [N, dv] that starts at zero:
+        S  <- exp(-exp(A_log_h) dt) S + dt B_t x_t^T
+        y_t = S^T C_t + D_h x_t
+    and out = Wo norm(y * silu(z)), the norm an RMS norm over each of ``norm_groups`` equal parts of
+    the row, times a weight.
+
+    What a sequence carries from step to step is of fixed size: the convolution's last taps - 1 inputs
+    and S of every head, both 32-bit.  The convolution, dt, the decay, the recurrence, the gate and the
+    norm are 32-bit arithmetic in both dtypes; the bfloat16 path rounds the input of the two
+    projections."""
+
+    category, kind = "mixer", "ssd"
+    graph_safe = True
+    default_names = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "a_log": "A_log",
+                     "d": "D", "norm": "norm", "o": "o"}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.dv, self.n = int(p["num_heads"]), int(p["value_dim"]), int(p["state_size"])
+        self.groups, self.norm_groups = int(p.get("groups", 1)), int(p.get("norm_groups", 1))
+        self.taps = int(p["taps"])
+        self.eps = float(p["eps"])
+        self.inner = self.nh * self.dv
+        self.channels = self.inner + 2 * self.groups * self.n
+        if self.nh % self.groups or self.inner % self.norm_groups:
+            raise ValueError("ssd: heads must be a multiple of groups, and heads * value_dim of norm_groups")
+        if not (0 < self.n <= 256 and 1 <= self.taps <= 16):
+            raise ValueError(f"ssd: state of {self.n}, {self.taps} taps; the kernels take up to 256 and 1 to 16")
+
+    def tensors(self):
+        n = self.names
+        return {
+            n["in"]: TensorSpec((2 * self.inner + 2 * self.groups * self.n + self.nh, self.hidden)),
+            n["conv"]: TensorSpec((self.channels, self.taps)),
+            n["conv_bias"]: TensorSpec((self.channels,), init="zeros", vector=True),
+            n["dt_bias"]: TensorSpec((self.nh,), init="zeros", vector=True),
+            n["a_log"]: TensorSpec((self.nh,), init="zeros", vector=True),
+            n["d"]: TensorSpec((self.nh,), init="ones", vector=True),
+            n["norm"]: TensorSpec((self.inner,), init="ones", vector=True),
+            n["o"]: TensorSpec((self.hidden, self.inner)),
+        }
+
+    def describe(self):
+        return (f"ssd({self.nh} heads of {self.dv}, state {self.n}x{self.dv} a head, {self.groups} groups, "
+                f"convolution of {self.taps} taps, norm in {self.norm_groups} parts)")
+
+    def kv_request(self):
+        return None
+
+    def state_request(self):
+        # [the convolution's last taps - 1 inputs | S of every head]
+        return StateRequest(((self.taps - 1) * self.channels + self.nh * self.n * self.dv,), torch.float32)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        n = self.names
+        self.w_in = tensors[n["in"]].contiguous()
+        self.taps_w = tensors[n["conv"]].to(torch.float32).t().contiguous()          # [taps, channels]
+        self.conv_b = tensors[n["conv_bias"]].to(torch.float32).contiguous()
+        self.dt_bias = tensors[n["dt_bias"]].to(torch.float32).contiguous()
+        self.a_log = tensors[n["a_log"]].to(torch.float32).contiguous()
+        self.d_skip = tensors[n["d"]].to(torch.float32).contiguous()
+        self.norm_w = tensors[n["norm"]].to(torch.float32).contiguous()
+        self.wo = tensors[n["o"]].contiguous()
+
+    def forward(self, rt, h, batch, cache_view, state):
+        T, I, C = batch.num_tokens, self.inner, self.channels
+        proj = linear(rt, h.act, self.w_in)                       # float32 [T, z | x B C | dt]
+        mixed = proj[:, I:I + C]
+        xbc = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+        core.seq_conv([dict(u=mixed, w=self.taps_w, bias=self.conv_b, offset=0, out32=xbc)], state, batch,
+                      taps=self.taps, channels=C, act="silu")
+        if self.taps > 1 and not batch.all_decode:
+            core.conv_state_update(mixed, state, batch, taps=self.taps, channels=C)
+        y = torch.empty((T, I), dtype=torch.float32, device=proj.device)
+        core.ssd_scan(xbc, proj[:, I + C:I + C + self.nh], self.dt_bias, self.a_log, self.d_skip, state, batch, y,
+                      heads=self.nh, groups=self.groups, n=self.n, dv=self.dv, offset=(self.taps - 1) * C)
+        out = rt.empty((T, I))
+        core.ssd_finish(y, proj[:, :I], self.norm_w, self.eps, batch, out, norm_groups=self.norm_groups)
+        return linear(rt, out, self.wo)
+
+
+class _SubTensors:
+    """The tensors of a part that lives inside another: local names with the inner prefix taken off."""
+
+    def __init__(self, outer, prefix, names):
+        self._outer, self._prefix, self._names = outer, prefix, list(names)
+
+    def __getitem__(self, local):
+        return self._outer[self._prefix + local]
+
+    def __contains__(self, local):
+        return local in self._names
+
+    def __iter__(self):
+        return iter(self._names)
+
+    def __len__(self):
+        return len(self._names)
+
+    def pop(self, local, *default):
+        if local not in self._names and default:
+            return default[0]
+        return self[local]
+
+
+class SideBySideMixer(Part):
+    """Two mixers that read the same input; each output passes an RMS norm over the model's width with
+    a weight of its own, and the result is half their sum:
+        out = (rmsnorm(left(n)) * w_left + rmsnorm(right(n)) * w_right) / 2
+    ``left`` and ``right`` are mixers of any registered kind ({"kind", "params"}); their tensors live
+    under ``left.`` / ``right.``.  At most one of them may keep keys and values in pages; state of fixed
+    size of both lies side by side in one row a sequence."""
+
+    category, kind = "mixer", "side_by_side"
+    default_names = {"left_out": "left.out", "right_out": "right.out"}
+
+    def __init__(self, spec):
+        from ..config.spec import PartSpec
+        from .base import make_part
+
+        super().__init__(spec)
+        p = self.params
+        self.hidden = int(p["hidden_size"])
+        self.eps = float(p["eps"])
+        self.subs = []
+        for side in ("left", "right"):
+            sub = p[side]
+            self.subs.append((side + ".", make_part("mixer", PartSpec(sub["kind"], dict(sub["params"]), spec.prefix + side + "."))))
+        self.graph_safe = all(getattr(m, "graph_safe", False) for _, m in self.subs)
+        self.wants32 = any(getattr(m, "wants32", False) for _, m in self.subs)
+        if sum(m.kv_request() is not None for _, m in self.subs) > 1:
+            raise ValueError("side_by_side: only one of the two mixers may keep keys and values in pages")
+        if not all(getattr(m, "own_kv", True) for _, m in self.subs):
+            raise ValueError("side_by_side: a mixer that reads another layer's cache cannot stand inside")
+
+    def _sub_tensors(self, fn):
+        t = {}
+        for prefix, m in self.subs:
+            for local, ts in fn(m, prefix).items():
+                t[prefix + local] = ts
+        n = self.names
+        t[n["left_out"]] = TensorSpec((self.hidden,), init="ones", vector=True)
+        t[n["right_out"]] = TensorSpec((self.hidden,), init="ones", vector=True)
+        return t
+
+    def tensors(self):
+        return self._sub_tensors(lambda m, prefix: m.tensors())
+
+    def tensors_in(self, has):
+        return self._sub_tensors(lambda m, prefix: m.tensors_in(lambda local: has(prefix + local)))
+
+    def describe(self):
+        return "half the sum of two normed mixers: " + " | ".join(m.describe() for _, m in self.subs)
+
+    def step_elements(self, num_tokens):
+        return float(sum(m.step_elements(num_tokens) for _, m in self.subs) + 2 * self.hidden)
+
+    def kv_request(self):
+        for _, m in self.subs:
+            if m.kv_request() is not None:
+                return m.kv_request()
+        return None
+
+    def state_request(self):
+        reqs = [m.state_request() for _, m in self.subs]
+        if all(r is None for r in reqs):
+            return None
+        n = 0
+        for r in reqs:
+            if r is not None:
+                if r.dtype != torch.float32 or len(r.shape) != 1:
+                    raise ValueError("side_by_side: the mixers' state must be rows of 32-bit floats")
+                n += r.shape[0]
+        return StateRequest((n,), torch.float32)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        for prefix, m in self.subs:
+            names = [k[len(prefix):] for k in tensors if k.startswith(prefix) and k not in self.names.values()]
+            m.bind(_SubTensors(tensors, prefix, names), rt)
+        self.w_left = tensors[self.names["left_out"]].to(torch.float32).contiguous()
+        self.w_right = tensors[self.names["right_out"]].to(torch.float32).contiguous()
+
+    def forward(self, rt, h, batch, cache_view, state):
+        outs, at = [], 0
+        for _, m in self.subs:
+            r = m.state_request()
+            sub_state = None
+            if r is not None:
+                sub_state = state[:, at:at + r.shape[0]]
+                at += r.shape[0]
+            outs.append(m.forward(rt, h, batch, cache_view if m.kv_request() is not None else None, sub_state))
+        out = torch.empty_like(outs[0])
+        core.pair_norm_mean(outs[0], self.w_left, outs[1], self.w_right, self.eps, out)
+        return out
+
+
+register_part("mixer", "ssd", SSDMixer)
+register_part("mixer", "side_by_side", SideBySideMixer)

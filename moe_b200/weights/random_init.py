@@ -30,6 +30,13 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 def _draw(name: str, ts, seed: int, std: float, dtype, device, norm_jitter: float, gen) -> torch.Tensor:
     gen.manual_seed(_tensor_seed(seed, name))
+    if getattr(ts, "integer", 0):
+        # every row: distinct numbers below ``integer``, in random order
+        rows = 1
+        for d in ts.shape[:-1]:
+            rows *= d
+        order = torch.rand((rows, ts.integer), generator=gen, dtype=torch.float32, device=device).argsort(dim=1)
+        return order[:, :ts.shape[-1]].reshape(ts.shape).to(torch.int32)
     if ts.init == "ones":
         t = torch.ones(ts.shape, dtype=torch.float32, device=device)
         if norm_jitter:

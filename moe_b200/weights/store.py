@@ -93,7 +93,10 @@ class WeightStore:
         t = t.to(device=device, copy=True) if str(device) == "cpu" else t.to(device=device)
         return t.contiguous()
 
-    def check(self, expected: Dict[str, Tuple[int, ...]], ignorable: Iterable[str] = ()) -> None:
+    def check(self, expected: Dict[str, Tuple[int, ...]], ignorable: Iterable[str] = (),
+              integer: Iterable[str] = ()) -> None:
+        """``integer``: the expected names that hold integer tables (every other one holds floats)."""
+        integer = set(integer)
         have = set(self.names())
         missing = sorted(n for n in expected if n not in have)
         patterns = list(ignorable)
@@ -107,7 +110,7 @@ class WeightStore:
                 # (an expected extent of -1 is one that only the tensor itself gives)
                 if len(got) != len(tuple(shp)) or any(e != -1 and e != g for g, e in zip(got, shp)):
                     wrong.append((n, got, tuple(shp)))
-                if self.stored_dtype(n) not in _FLOATS:
+                if (self.stored_dtype(n) not in _FLOATS) != (n in integer):
                     wrong_dt.append((n, str(self.stored_dtype(n))))
         if missing or unexpected or wrong or wrong_dt:
             raise WeightError(missing, unexpected, sorted(wrong), sorted(wrong_dt))
