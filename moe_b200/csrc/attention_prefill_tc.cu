@@ -412,6 +412,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             return cap_log2 * (1.0f - __fdividef(2.0f, e + 1.0f));
         };
         const uint32_t to = tmem + COL_O + lane_base + half * (HD / 2);
+        // weights sigmoid(score + b_h) instead of a softmax: no maximum, no sum, no division at the end
+        const bool sigmoid_w = av.sink == ATTN_SIGMOID;
+        const float bias_log2 = sigmoid_w ? attn_sink_value(av, head) * 1.4426950408889634f : 0.f;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int it = 0; it < n_tiles; it++) {
@@ -431,6 +434,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             auto tile_softmax = [&](auto masked_tag) -> bool {
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 auto visible = [&](int j) { return j <= prow && j < jmax && j >= lo_row; };
+                float m_new = m, alpha = 1.f;
+                if (!sigmoid_w) {
                 // pass 1: the maximum of the half row (of the raw scores: the scale is positive)
                 float mx0 = -INFINITY, mx1 = -INFINITY;
                 {
@@ -457,7 +462,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 const float mx = av.softcap > 0.f ? (mx_raw == -INFINITY ? -INFINITY : capped(mx_raw)) : mx_raw * scale_log2;
                 // The running maximum only has to keep the exponentials in range: it moves when the
                 // tile's maximum exceeds it by more than 8 (a factor 256), which spares most rescalings.
-                float m_new = m, alpha = 1.f;
                 if (mx > m + 8.f || m == -INFINITY) {
                     m_new = fmaxf(m, mx);
                     alpha = (m == -INFINITY) ? 1.f : ex2_approx(m - m_new);     // nothing accumulated yet: nothing to rescale
@@ -478,6 +482,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         for (int i = 0; i < 32; i++) t[i] *= alpha;
                         tmem_st32(to + c * 32, t);
                     }
+                }
+                } else {
+                    m_new = 0.f;       // sigmoid weights need no common shift: nothing is exchanged or rescaled
                 }
                 // pass 2: P in two bfloat16 terms, into tensor memory (two keys per 32-bit column), 32
                 // scores at a time, read again (they are not kept over the exchange above: registers)
@@ -501,7 +508,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                             if (!visible(jh + c * 32 + i)) x0 = -INFINITY;
                             if (!visible(jh + c * 32 + i + 1)) x1 = -INFINITY;
                         }
-                        const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                        // (sigmoid weights: 1 / (1 + 2^-(score + bias)), 0 for a key out of sight)
+                        const float p0 = sigmoid_w ? __fdividef(1.0f, 1.0f + ex2_approx(-(x0 + bias_log2))) : ex2_approx(x0);
+                        const float p1 = sigmoid_w ? __fdividef(1.0f, 1.0f + ex2_approx(-(x1 + bias_log2))) : ex2_approx(x1);
                         rs += p0, rs1 += p1;
                         const uint32_t h = pack_bf16(p0, p1);
                         hi[i / 2] = h;
@@ -522,10 +531,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             if (lane == 0) mbar_arrive(p_full);       // P is in place, and the output row is rescaled
         }
         // the row's sum: the two halves, in a fixed order
-        if (ok) {
+        if (ok && !sigmoid_w) {
             // (a sink: one more term, of score 0 or the head's own number, which carries no value; both
             // halves hold the same m, which is in units of log 2)
-            x_sum[half][r] = (av.sink && half == 0 && m != -INFINITY)
+            x_sum[half][r] = (av.sink == ATTN_SINK && half == 0 && m != -INFINITY)
                                  ? l + ex2_approx(attn_sink_value(av, head) * 1.4426950408889634f - m) : l;
             __syncwarp();
             if (lane == 0) mbar_arrive(x_bar(qd));
@@ -540,7 +549,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         } else {
             tc_fence_after();
             const float lsum = x_sum[0][r] + x_sum[1][r];
-            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            const float inv = sigmoid_w ? 1.f : lsum > 0.f ? 1.f / lsum : 0.f;
             uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(tok0 + min(row, len - 1)) * nh + head) * HD +
                                                   half * (HD / 2));
 #pragma unroll

@@ -699,8 +699,6 @@ class SigmoidWeights:
     weights are not normalised over the keys (``bias``: float32 [heads] or None)."""
 
     def __init__(self, bias=None):
-        if bias is not None:
-            _chk(bias, "head bias", torch.float32, 1)
         self.bias = bias
 
 
@@ -712,6 +710,8 @@ def _variant(chunk, softcap, sink):
     csrc/common.cuh.  ``sink``: False, True (a term of score 0), a float32 tensor with one number
     per query head (the term's own score), or ``SigmoidWeights``."""
     if isinstance(sink, SigmoidWeights):
+        if sink.bias is not None:
+            _chk(sink.bias, "head bias", torch.float32, 1)
         return int(chunk or 0), float(softcap or 0.0), ATTN_SIGMOID, _p(sink.bias)
     if isinstance(sink, torch.Tensor):
         _chk(sink, "sink", torch.float32, 1)

@@ -361,7 +361,7 @@ class GQAttention(Part):
             return linear(rt, packed, self.wo, bias=self.bo)
         else:
             done = False
-            if rt.is_bf16 and not self.sigmoid:
+            if rt.is_bf16:
                 from ..ops import tc
 
                 if batch.all_fresh:

@@ -120,7 +120,8 @@ def chunked_sigmoid_attention(q, k, v, scale, chunk, head_bias):
 def attention_mixer(w, p, m, n, eps):
     """The attention mixer on n [T, width]; p is the tensor prefix '<layer>.mix.left'."""
     T = n.shape[0]
-    H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+    H, d = int(m["heads"]), int(m["dim"])
+    G, dv = int(m.get("kv_heads") or H), int(m.get("vdim") or d)
     pos = torch.arange(T)
     # one RMS norm over the whole projection, all heads at once
     q = (unit_rms(n @ w[p + ".q"].T, eps) * w[p + ".q.norm"]).reshape(T, H, d)
