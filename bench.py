@@ -844,6 +844,261 @@ def run_fogapel(args):
     return 0
 
 
+# Divadra at sizes that resemble a real model's layers, and beside each the library's closest model at
+# equal size: Fogapel (parallel blocks, chunked attention, the same recurrent mixer, dense and routed
+# feed-forwards) with as many layers, the same width, heads, head size, chunks, experts, expert size
+# and vocabulary; an attention layer where Divadra runs attention beside the recurrent mixer, a
+# recurrent layer where Divadra has the state-space mixer.
+DIVADRA_SHAPES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, chunk=1024, rot=64, taps=4, wkv_heads=32, wkv_dim=64,
+                  ssd_heads=32, ssd_vdim=64, state=128, groups=1, norm_groups=1, conv=4, ff=5632, experts=32, top=4,
+                  expert_ff=704, order=("parallel", "mamba2", "parallel", "parallel", "mamba2", "parallel"), vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, chunk=2048, rot=64, taps=4, wkv_heads=64, wkv_dim=64,
+                  ssd_heads=64, ssd_vdim=64, state=128, groups=1, norm_groups=1, conv=4, ff=11008, experts=32, top=4,
+                  expert_ff=1408, order=("parallel", "mamba2", "parallel", "mamba2"), vocab=32768),
+}
+
+
+def divadra_config(sh):
+    left = {"heads": sh["heads"], "kv_heads": sh["kv_heads"], "dim": sh["dim"], "vdim": sh["vdim"], "scale": sh["dim"] ** -0.5,
+            "mask": {"size": sh["chunk"]}, "rot": {"dims": sh["rot"], "base": 1e6}}
+    par = {"left": left, "right": {"heads": sh["wkv_heads"], "dim": sh["wkv_dim"]}}
+    ssd = {"heads": sh["ssd_heads"], "vdim": sh["ssd_vdim"], "state": sh["state"], "groups": sh["groups"],
+           "norm_groups": sh["norm_groups"], "conv": sh["conv"]}
+    moe = {"kind": "moe", "router": {"experts": sh["experts"], "top": sh["top"]}, "expert": {"ff": sh["expert_ff"]}}
+    dense = {"kind": "dense", "ff": sh["ff"]}
+    return {"architecture": "Divadra", "vocab": sh["vocab"], "width": sh["width"], "norm": {"eps": 1e-5},
+            "canon": {"taps": sh["taps"]}, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 40503, "mul_cur": 65599}},
+            "layers": [{"type": t, "mixer": par if t == "parallel" else ssd, "mlp": dense if i == 0 else moe}
+                       for i, t in enumerate(sh["order"])]}
+
+
+def divadra_fogapel_config(sh):
+    att = {"heads": sh["heads"], "kv_heads": sh["kv_heads"], "dim": sh["dim"], "vdim": sh["vdim"], "scale": sh["dim"] ** -0.5,
+           "softcap": 30.0, "conv": sh["taps"], "mask": {"size": sh["chunk"]}, "rot": {"dims": sh["rot"], "base": 1e6}}
+    wkv = {"heads": sh["wkv_heads"], "dim": sh["wkv_dim"]}
+    moe = {"kind": "moe", "router": {"experts": sh["experts"], "top": sh["top"]}, "expert": {"ff": sh["expert_ff"]}}
+    dense = {"kind": "dense", "ff": sh["ff"], "limit": 7.0}
+    return {"architecture": "Fogapel", "vocab": sh["vocab"], "width": sh["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention" if t == "parallel" else "wkv", "mixer": att if t == "parallel" else wkv,
+                        "mlp": dense if i == 0 else moe} for i, t in enumerate(sh["order"])]}
+
+
+def divadra_kernels(sh, pk):
+    """The new design's own kernels beside the like kernels of the closest model, each alone at 8,192
+    tokens of 4 sequences (what a call reads and writes exceeds L2), as a fraction of the measured copy
+    bandwidth (attention: of the measured bf16 peak, counting the products of the keys a query sees)."""
+    import torch
+
+    from moe_b200.ops import core, tc
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import gpu_util as G
+
+    dev = "cuda:0"
+    B, n = 4, 2048
+    T, H, nh, nkv, d = B * n, sh["width"], sh["heads"], sh["kv_heads"], sh["dim"]
+    status = core.new_status(dev)
+    r = lambda *s: torch.randn(*s, device=dev)
+    out = {}
+
+    def row(name, ms, nbytes=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if nbytes:
+            e["gb_s"] = round(nbytes / ms / 1e6, 0)
+            e["of_copy_peak"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 3)
+        if flops:
+            e["tflops"] = round(flops / ms / 1e9, 0)
+            e["of_bf16_peak"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 3)
+        out[name] = e
+
+    ids = torch.randint(0, sh["vocab"], (T,)).tolist()
+    batch = G.make_batch(dev, list(range(1, B + 1)), [0] * B, [n] * B, tokens=[ids[i * n:(i + 1) * n] for i in range(B)])
+    one = G.make_batch(dev, list(range(1, 65)), [n] * 64, [1] * 64)
+    # ---- embedding ----------------------------------------------------------------------------------
+    table = (torch.randn(sh["vocab"], H, device=dev)).to(torch.bfloat16)
+    pair = (torch.randn(65522, H, device=dev)).to(torch.bfloat16)
+    x, w = torch.empty((T, H), device=dev), r(H)
+    prev = torch.zeros((B + 2, 1), dtype=torch.int32, device=dev)
+    row("embed_pair (two rows + norm)", _median_ms(lambda: core.embed_pair(table, pair, w, 1e-5, batch, x, prev, buckets=65521,
+        mul_prev=40503, mul_cur=65599, status=status)), T * H * (2 + 2 + 4))
+    row("embed (one row)", _median_ms(lambda: core.embed(table, batch.token_ids, x, status)), T * H * (2 + 4))
+    # ---- norms and the input convolutions ---------------------------------------------------------------
+    a, b, ones = r(T, H), r(T, H), torch.ones(H, device=dev)
+    o16, o16b = (torch.empty((T, H), dtype=torch.bfloat16, device=dev) for _ in range(2))
+    o32, o32b = torch.empty((T, H), device=dev), torch.empty((T, H), device=dev)
+    row("rmsnorm_scaled (two outputs + sum + norm; the closest model's one norm a layer)",
+        _median_ms(lambda: core.rmsnorm_scaled(x, a, ones, b, ones, w, 1e-5, out16=o16, status=status)), T * H * (4 + 4 + 4 + 4 + 2))
+    row("rmsnorm (the second norm of the same stream)", _median_ms(lambda: core.rmsnorm(x, w, 1e-5, out32=o32, write_back=False, status=status)),
+        T * H * (4 + 4))
+    cstate = torch.zeros((B + 2, 2 * (sh["taps"] - 1) * H), device=dev)
+    tw = r(sh["taps"], H)
+    jobs = [dict(u=o32, w=tw, bias=None, offset=0, out32=a, out16=o16), dict(u=o32b, w=tw, bias=None, offset=(sh["taps"] - 1) * H, out16=o16b)]
+    row("seq_conv (both sublayers' inputs: h + conv(h))", _median_ms(lambda: core.seq_conv(jobs, cstate, batch, taps=sh["taps"], channels=H,
+        residual=True)), T * H * (4 + 4 + 2 + 4 + 2))
+    # ---- between projection and attention -------------------------------------------------------------
+    wq = (nh + 2 * nkv) * d
+    proj = r(T, wq)
+    q, k, v = (torch.empty((T, m, d), dtype=torch.bfloat16, device=dev) for m in (nh, nkv, nkv))
+    freq, vfreq = torch.rand(sh["rot"] // 2, device=dev), torch.rand(d // 2, device=dev)
+    qn, kn = r(nh * d), r(nkv * d)
+    row("whole_prepare (norm over the projection + rotations of q, k, v + split)", _median_ms(lambda: core.whole_prepare(
+        proj, batch, nh=nh, nkv=nkv, d=d, dv=d, width=d, q=q, k=k, v=v, q_norm=qn, k_norm=kn, eps=1e-5, freq=freq, rot=sh["rot"],
+        vfreq=vfreq, status=status)), T * wq * (4 + 2))
+    taps_w = r(sh["taps"], wq)
+    state = torch.zeros((B + 2, (sh["taps"] - 1) * wq), device=dev)
+    row("conv_heads_prepare (the closest model's: convolution + rotation + unit norm + split)", _median_ms(lambda: core.conv_heads_prepare(
+        proj, batch, nh=nh, nkv=nkv, d=d, dv=d, width=d, q=q, k=k, v=v, taps_w=taps_w, state=state, eps=1e-5, unit_norm=True,
+        freq=freq, rot=sh["rot"], status=status)), T * wq * (4 + 2))
+    # ---- attention of whole prompts: keys a query sees, 4 flops a key and dimension -------------------------
+    qq, kk, vv = (torch.randn(T, m, d, device=dev).to(torch.bfloat16) for m in (nh, nkv, nkv))
+    ctx = torch.empty((T, nh, d), dtype=torch.bfloat16, device=dev)
+    c = sh["chunk"]
+    seen = sum(p % c + 1 for p in range(n)) * B
+    hb = r(nh)
+    row("tcgen05 attention, chunks + sigmoid weights", _median_ms(lambda: tc.attention_prefill(
+        qq, kk, vv, batch, ctx, nh=nh, nkv=nkv, hd=d, window=None, scale=d ** -0.5, status=status, chunk=c,
+        sink=core.SigmoidWeights(hb))), flops=4.0 * seen * nh * d)
+    row("tcgen05 attention, chunks + capped scores + sink (the closest model's)", _median_ms(lambda: tc.attention_prefill(
+        qq, kk, vv, batch, ctx, nh=nh, nkv=nkv, hd=d, window=None, scale=d ** -0.5, status=status, chunk=c, softcap=30.0,
+        sink=True)), flops=4.0 * seen * nh * d)
+    packed = torch.empty((T, nh * d), dtype=torch.bfloat16, device=dev)
+    row("unrotate_pack (the turn back of the heads' outputs)", _median_ms(lambda: core.unrotate_pack(ctx, batch.pos, vfreq, packed, nh=nh,
+        dv=d, width=d)), T * nh * d * (2 + 2))
+    # ---- single tokens over the cache ---------------------------------------------------------------------
+    # ---- the two mixers' outputs into one --------------------------------------------------------------------
+    row("pair_norm_mean (two norms + half the sum)", _median_ms(lambda: core.pair_norm_mean(a, w, b, w, 1e-5, o32)), T * H * 12)
+    # ---- the state-space mixer beside the recurrent one ------------------------------------------------------
+    sheads, sdv, N, G_ = sh["ssd_heads"], sh["ssd_vdim"], sh["state"], sh["groups"]
+    inner, ch = sheads * sdv, sheads * sdv + 2 * G_ * sh["state"]
+    pin = r(T, 2 * inner + 2 * G_ * N + sheads)
+    xbc = torch.empty((T, ch), device=dev)
+    sstate = torch.zeros((B + 2, (sh["conv"] - 1) * ch + sheads * N * sdv), device=dev)
+    cw, cb = r(sh["conv"], ch), r(ch)
+    row("seq_conv with bias and silu (x, B, C of the state-space mixer)", _median_ms(lambda: core.seq_conv(
+        [dict(u=pin[:, inner:inner + ch], w=cw, bias=cb, offset=0, out32=xbc)], sstate, batch, taps=sh["conv"], channels=ch, act="silu")),
+        T * ch * 8)
+    dtb, alog, dsk = r(sheads), r(sheads) - 1, r(sheads)
+    y = torch.empty((T, inner), device=dev)
+    off = (sh["conv"] - 1) * ch
+    ms = _median_ms(lambda: core.ssd_scan(xbc, pin[:, inner + ch:], dtb, alog, dsk, sstate, batch, y, heads=sheads, groups=G_, n=N,
+                                          dv=sdv, offset=off))
+    row("ssd_scan (4 sequences of 2,048 tokens)", ms, T * (ch + inner) * 4, flops=4.0 * T * inner * N)
+    out["ssd_scan (4 sequences of 2,048 tokens)"]["us_per_token_of_a_sequence"] = round(ms * 1e3 / n, 3)
+    st64 = torch.zeros((66, off + sheads * N * sdv), device=dev)
+    x1, p1, y1 = r(64, ch), r(64, 2 * inner + 2 * G_ * N + sheads), torch.empty((64, inner), device=dev)
+    row("ssd_scan (one token of 64 sequences: the state read and written)", _median_ms(lambda: core.ssd_scan(
+        x1, p1[:, inner + ch:], dtb, alog, dsk, st64, one, y1, heads=sheads, groups=G_, n=N, dv=sdv, offset=off)),
+        64 * sheads * N * sdv * 4 * 2)
+    y16 = torch.empty((T, inner), dtype=torch.bfloat16, device=dev)
+    nw = r(inner)
+    row("ssd_finish (gate + norm)", _median_ms(lambda: core.ssd_finish(y, pin[:, :inner], nw, 1e-5, batch, y16, norm_groups=sh["norm_groups"])),
+        T * inner * (4 + 4 + 2))
+    wh, wd = sh["wkv_heads"], sh["wkv_dim"]
+    I = wh * wd
+    rr, kk2, vv2, decay = r(T, I) / 8, r(T, I) / 8, r(T, I), torch.rand(T, I, device=dev)
+    o, u = torch.empty((T, I), device=dev), r(wh, wd)
+    wstate = torch.zeros((B + 2, H + I * wd), device=dev)
+    ms = _median_ms(lambda: core.wkv_scan(rr, kk2, vv2, decay, u, wstate[:, H:], batch, o, heads=wh, d=wd))
+    row("wkv_scan (the recurrent mixer's, 4 sequences of 2,048 tokens)", ms, T * I * 4 * 5, flops=6.0 * T * I * wd)
+    out["wkv_scan (the recurrent mixer's, 4 sequences of 2,048 tokens)"]["us_per_token_of_a_sequence"] = round(ms * 1e3 / n, 3)
+    st64w = torch.zeros((66, H + I * wd), device=dev)
+    r1 = lambda: (r(64, I) / 8)
+    a1, b1, c1, d1, o1 = r1(), r1(), r1(), torch.rand(64, I, device=dev), torch.empty((64, I), device=dev)
+    row("wkv_scan (one token of 64 sequences: the state read and written)",
+        _median_ms(lambda: core.wkv_scan(a1, b1, c1, d1, u, st64w[:, H:], one, o1, heads=wh, d=wd)), 64 * I * wd * 4 * 2)
+    yw = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
+    gate, nww = r(T, I), r(I)
+    row("wkv_finish (the recurrent mixer's head norm + gate)", _median_ms(lambda: core.wkv_finish(o, gate, nww, 1e-5, batch, yw, heads=wh, d=wd)),
+        T * I * (4 + 4 + 2))
+    # ---- the dense feed-forward's first product and activation ----------------------------------------------
+    a16 = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    wup = (torch.randn(sh["ff"], H, device=dev) / 32).to(torch.bfloat16)
+    wgu = (torch.randn(2 * sh["ff"], H, device=dev) / 32).to(torch.bfloat16)
+    act = torch.empty((T, sh["ff"]), dtype=torch.bfloat16, device=dev)
+
+    def up_relu2():
+        from moe_b200.parts.feedforward import relu2_linear
+
+        relu2_linear(_Rt(status), a16, wup, act)
+
+    row("up product with the squared relu", _median_ms(up_relu2), flops=2.0 * T * sh["ff"] * H)
+    row("gate|up product, clamped sigmoid epilogue (the closest model's)", _median_ms(lambda: tc.gemm_tc(
+        a16, wgu, act, swiglu=True, status=status, act="clamped_sigmoid", act_param=7.0)), flops=2.0 * T * 2 * sh["ff"] * H)
+    # ---- the experts' choice -------------------------------------------------------------------------------------
+    tbl = torch.rand(sh["vocab"], sh["experts"], device=dev).argsort(dim=1)[:, :sh["top"]].to(torch.int32).contiguous()
+    idx, wt = torch.empty((T, sh["top"]), dtype=torch.int32, device=dev), torch.empty((T, sh["top"]), device=dev)
+    row("table_route (experts by token id)", _median_ms(lambda: core.table_route(tbl, batch, sh["top"], sh["experts"], idx, wt, status)),
+        T * sh["top"] * 12)
+    core.check_status(status)
+    return out
+
+
+class _Rt:
+    """What ``ops.linear`` asks of a runtime, for calling a product outside a model."""
+
+    is_bf16 = True
+
+    def __init__(self, status):
+        import torch
+
+        self.status, self.compute_dtype = status, torch.bfloat16
+
+
+def run_divadra(args):
+    """``--workload divadra``: prefill and decode of the Divadra design at two sizes, the closest existing
+    model at equal size beside it, and the new kernels beside their counterparts.  One JSON line per
+    shape; not the benchmark record."""
+    import torch
+
+    import moe_b200
+
+    pk = peaks()
+    names = [args.shape] if args.shape in DIVADRA_SHAPES else list(DIVADRA_SHAPES)
+    for name in names:
+        sh = DIVADRA_SHAPES[name]
+        V = sh["vocab"]
+        res = {"workload": "divadra", "shape": name, "sizes": sh, "dtype": "bfloat16", "data": "synthetic, random weights",
+               "peaks": pk}
+        for label, cfg in (("divadra", divadra_config(sh)), ("fogapel", divadra_fogapel_config(sh))):
+            model = moe_b200.random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+            r = {"parameters": int(model.num_parameters)}
+            eng = moe_b200.Engine(model, max_tokens=64 * (512 + args.steps + 64) + 4096, max_slots=64)
+            ids = [(i * 7 + 13) % V for i in range(PREFILL_TOKENS)]
+
+            def prefill():
+                s = eng.new_sequence()
+                eng.step([s], [ids], check=False)
+                eng.release(s)
+
+            ms = _median_ms(prefill)
+            r["prefill_2048"] = {"ms": round(ms, 3), "tokens_per_s": round(PREFILL_TOKENS / ms * 1e3, 0)}
+            for B in (1, 8, 64):
+                slots = [eng.new_sequence() for _ in range(B)]
+                eng.step(slots, [ids[:PROMPT_LEN]] * B, check=False)
+                for i in range(args.warmup):
+                    eng.step(slots, [[i % V]] * B, check=False)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                for i in range(args.steps):
+                    eng.step(slots, [[(i + 5) % V]] * B, check=False)
+                b.record()
+                torch.cuda.synchronize()
+                eng.rt.check()
+                ms = a.elapsed_time(b) / args.steps
+                r[f"decode_b{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 0)}
+                for s in slots:
+                    eng.release(s)
+            res[label] = r
+            del eng, model
+            torch.cuda.empty_cache()
+        res["kernels_at_8192_tokens"] = divadra_kernels(sh, pk)
+        print(json.dumps(res), flush=True)
+    return 0
+
+
 # Zosipel at sizes that resemble a real model's layers, and beside each the library's closest model at
 # equal size: Qwen2 MoE with as many layers as the Zosipel shape has layer RUNS, the same width, heads,
 # experts, expert and shared sizes and vocabulary, every layer routed, heads of twice a map's size (a
@@ -1095,12 +1350,12 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="with --profile-step decode: sequences in the batch")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="with --profile-step: the path whose kernels are wanted")
-    ap.add_argument("--shape", choices=["a2.7b", "57b"] + sorted(set(SUPEVIK_SHAPES) | set(FOGAPEL_SHAPES) | set(ZOSIPEL_SHAPES)), default="a2.7b",
-                    help="with --sweep: the layer sizes; with --workload supevik, fogapel or zosipel: one of its shapes (default: all)")
+    ap.add_argument("--shape", choices=["a2.7b", "57b"] + sorted(set(SUPEVIK_SHAPES) | set(FOGAPEL_SHAPES) | set(ZOSIPEL_SHAPES) | set(DIVADRA_SHAPES)), default="a2.7b",
+                    help="with --sweep: the layer sizes; with --workload supevik, fogapel, zosipel or divadra: one of its shapes (default: all)")
     ap.add_argument("--prompt-len", type=int, default=0, help="with --sweep: tokens in each prompt (default 512)")
-    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt", "supevik", "fogapel", "zosipel"], default=None,
+    ap.add_argument("--workload", choices=["fp32-32k", "long-prompt", "supevik", "fogapel", "zosipel", "divadra"], default=None,
                     help="fp32-32k: the true 32-bit path at a context of 32,768; long-prompt: one bfloat16 prompt of "
-                         "--prompt-len tokens [32768] run in pieces; supevik, fogapel, zosipel: that design at two sizes beside "
+                         "--prompt-len tokens [32768] run in pieces; supevik, fogapel, zosipel, divadra: that design at two sizes beside "
                          "the closest model at equal size (each prints its own line, no benchmark record)")
     ap.add_argument("--unequal", action="store_true", help="with --sweep: prompts of unequal lengths, 256 to 2,048 tokens")
     ap.add_argument("--sweep", default=None, help="comma-separated batch sizes: print decode throughput for each "
@@ -1126,6 +1381,8 @@ def main():
         return run_fogapel(args)
     if args.workload == "zosipel":
         return run_zosipel(args)
+    if args.workload == "divadra":
+        return run_divadra(args)
     return run_ours(args)
 
 

@@ -79,7 +79,15 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 // The gate's activation of a gated feed-forward, act(g) * u.  ACT_CLAMPED_SIGMOID has a constant
 // `param` (the limit L): g' = min(g, L), u' = clamp(u, -L, L), g' sigmoid(1.702 g') (u' + 1).
-enum : int { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_CLAMPED_SIGMOID = 2 };
+// ACT_RELU2 is no gate's activation: an ungated product's output passes relu(x)^2 (plain_act).
+enum : int { ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_CLAMPED_SIGMOID = 2, ACT_RELU2 = 3 };
+__device__ __forceinline__ float plain_act(int act, float v) {
+    if (act == ACT_RELU2) {
+        v = fmaxf(v, 0.f);
+        return v * v;
+    }
+    return v;
+}
 __device__ __forceinline__ float glu_mul(int act, float param, float g, float u) {
     if (act == ACT_GELU_TANH)      // 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
         return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;

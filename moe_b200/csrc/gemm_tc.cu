@@ -14,7 +14,7 @@
 //   warps 2-5   epilogue: tensor memory -> registers -> global memory
 //
 // Modes
-//   PLAIN    out[t, n] = acc (+ bias[n]); out is float32 or bfloat16
+//   PLAIN    out[t, n] = f(acc (+ bias[n])); out is float32 or bfloat16; f is the identity, or relu(.)^2 with ACT_RELU2
 //   SWIGLU   W holds gate rows [0, I) and up rows [I, 2I) per group; two accumulators;
 //            out[t, j] = silu(gate) * up  (reference: src/model.rs:26-35)
 // Groups (routed experts): rows of X are partitioned by group_offsets[G + 1]; group g
@@ -474,7 +474,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     for (int j = 0; j < 16; j++) {
                         const int t = row0 + c0 + j;
                         if (n_ok && t < row_end) {
-                            const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], b[j]) : a[j] + bias;
+                            const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], b[j]) : plain_act(p.act, a[j] + bias);
                             if (p.out_bf16)
                                 ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
                             else
@@ -541,7 +541,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                                     sa += va[r][s];
                                     if (MODE == MODE_SWIGLU) sb += vb[r][s];
                                 }
-                                const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, sa, sb) : sa + bias;
+                                const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, sa, sb) : plain_act(p.act, sa + bias);
                                 if (p.out_bf16)
                                     ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(v);
                                 else
@@ -592,7 +592,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                         sa += va[r][s];
                         if (MODE == MODE_SWIGLU) sb += vb[r][s];
                     }
-                    const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, sa, sb) : sa + bias;
+                    const float v = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, sa, sb) : plain_act(p.act, sa + bias);
                     if (p.out_bf16)
                         ((__nv_bfloat16*)p.out)[(size_t)(row0 + t) * p.ldo + n] = __float2bfloat16_rn(v);
                     else
@@ -631,13 +631,13 @@ __device__ __forceinline__ void epilogue_part(const Params& p, uint32_t taddr, i
 #pragma unroll
             for (int j = 0; j < 32; j++)
                 if (n_ok && row0 + c0 + j < row_end)
-                    o[(size_t)j * p.ldo] = __float2bfloat16_rn(MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], bb[j]) : a[j] + bias);
+                    o[(size_t)j * p.ldo] = __float2bfloat16_rn(MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], bb[j]) : plain_act(p.act, a[j] + bias));
         } else {
             float* o = (float*)p.out + (size_t)(row0 + c0) * p.ldo + n;
 #pragma unroll
             for (int j = 0; j < 32; j++)
                 if (n_ok && row0 + c0 + j < row_end)
-                    o[(size_t)j * p.ldo] = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], bb[j]) : a[j] + bias;
+                    o[(size_t)j * p.ldo] = MODE == MODE_SWIGLU ? glu_mul(p.act, p.act_param, a[j], bb[j]) : plain_act(p.act, a[j] + bias);
         }
     }
 }

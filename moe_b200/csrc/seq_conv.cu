@@ -35,38 +35,81 @@ struct ConvJobs {
     ConvJob j[2];
 };
 
-// grid (token, channel block, job); a thread a channel.
+__device__ __forceinline__ void sc_store(float* o32, __nv_bfloat16* o16, size_t at, const float (&y)[4], int n) {
+    if (n == 4) {
+        if (o32) *reinterpret_cast<float4*>(o32 + at) = make_float4(y[0], y[1], y[2], y[3]);
+        if (o16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+            uint2 u;
+            u.x = *reinterpret_cast<unsigned*>(&lo), u.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(o16 + at) = u;
+        }
+    } else {
+        for (int e = 0; e < n; e++) {
+            if (o32) o32[at + e] = y[e];
+            if (o16) o16[at + e] = __float2bfloat16_rn(y[e]);
+        }
+    }
+}
+
+// grid (token, channel block, job).  VEC: a thread takes four neighbouring channels 16 bytes at a time;
+// else one channel.  Nothing is kept in an array over the taps: a tap's input is used, moved one place
+// down in the state where the step brings one row a sequence (`shift`: the place was read a tap ago), and
+// forgotten.
+template <bool VEC, int TAPS, int TOKB>
 __global__ void __launch_bounds__(256)
-seq_conv_kernel(const ConvJobs jobs, int taps, int channels, long long state_pitch,
-                const int* __restrict__ seq_of_token, const int* __restrict__ pos, const int* __restrict__ cu_seqlens,
-                const int* __restrict__ slots, int residual, int act, int shift) {
+seq_conv_kernel(const ConvJobs jobs, int taps_any, int channels, long long state_pitch,
+                const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens,
+                const int* __restrict__ slots, int num_tokens, int residual, int act, int shift) {
+    constexpr int W = VEC ? 4 : 1;
+    const int taps = TAPS > 0 ? TAPS : taps_any;      // (a number known when compiled: the taps' loads are all in flight at once)
     pdl_sync();
     const ConvJob& J = jobs.j[blockIdx.z];
-    const int t = blockIdx.x;
-    const int ch = blockIdx.y * blockDim.x + threadIdx.x;
+    const int ch = (blockIdx.y * blockDim.x + threadIdx.x) * W;
     if (ch >= channels) return;
-    const int s = seq_of_token[t];
-    if (s < 0) {          // a row of no sequence: something finite, no state touched
-        if (J.out32) J.out32[(size_t)t * channels + ch] = 0.f;
-        if (J.out16) J.out16[(size_t)t * channels + ch] = __float2bfloat16_rn(0.f);
-        return;
+    // TOKB rows a block (many rows: fewer, longer blocks with more loads in flight a thread)
+#pragma unroll
+    for (int tt = 0; tt < TOKB; tt++) {
+        const int t = blockIdx.x * TOKB + tt;
+        if (t >= num_tokens) break;
+        const int s = seq_of_token[t];
+        const size_t oat = (size_t)t * channels + ch;
+        float y[4] = {0.f, 0.f, 0.f, 0.f};
+        if (s < 0) {          // a row of no sequence: something finite, no state touched
+            sc_store(J.out32, J.out16, oat, y, W);
+            continue;
+        }
+        const int li = t - cu_seqlens[s];                 // the row's place among the sequence's rows of this step
+        float* st = taps > 1 ? J.state + (size_t)slots[s] * state_pitch : nullptr;
+        if (J.bias) {
+#pragma unroll
+            for (int e = 0; e < W; e++) y[e] = J.bias[ch + e];
+        }
+        float own[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int j = 0; j < taps; j++) {
+            const int r = li - (taps - 1) + j;            // the row tap j reads, relative to the step's first
+            const float* src = r >= 0 ? J.u + (size_t)(t - li + r) * J.ldu + ch : st + (size_t)(taps - 1 + r) * channels + ch;
+            const float* wj = J.w + (size_t)j * channels + ch;
+            if (VEC) {
+                const float4 x4 = *reinterpret_cast<const float4*>(src), w4 = *reinterpret_cast<const float4*>(wj);
+                own[0] = x4.x, own[1] = x4.y, own[2] = x4.z, own[3] = x4.w;
+                y[0] = fmaf(w4.x, x4.x, y[0]), y[1] = fmaf(w4.y, x4.y, y[1]);
+                y[2] = fmaf(w4.z, x4.z, y[2]), y[3] = fmaf(w4.w, x4.w, y[3]);
+                if (shift && j >= 1) *reinterpret_cast<float4*>(st + (size_t)(j - 1) * channels + ch) = x4;
+            } else {
+                own[0] = *src;
+                y[0] = fmaf(*wj, own[0], y[0]);
+                if (shift && j >= 1) st[(size_t)(j - 1) * channels + ch] = own[0];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < W; e++) {
+            if (act == SC_ACT_SILU) y[e] = y[e] / (1.0f + expf(-y[e]));
+            if (residual) y[e] += own[e];
+        }
+        sc_store(J.out32, J.out16, oat, y, W);
     }
-    const int li = t - cu_seqlens[s];                 // the row's place among the sequence's rows of this step
-    float* st = J.state + (size_t)slots[s] * state_pitch;
-    float x[SC_MAX_TAPS];
-#pragma unroll 4
-    for (int j = 0; j < taps; j++) {
-        const int r = li - (taps - 1) + j;            // the row tap j reads, relative to the step's first
-        x[j] = r >= 0 ? J.u[(size_t)(t - li + r) * J.ldu + ch] : st[(size_t)(taps - 1 + r) * channels + ch];
-    }
-    float y = J.bias ? J.bias[ch] : 0.f;
-    for (int j = 0; j < taps; j++) y = fmaf(J.w[(size_t)j * channels + ch], x[j], y);
-    if (act == SC_ACT_SILU) y = y / (1.0f + expf(-y));
-    if (residual) y += x[taps - 1];
-    if (J.out32) J.out32[(size_t)t * channels + ch] = y;
-    if (J.out16) J.out16[(size_t)t * channels + ch] = __float2bfloat16_rn(y);
-    if (shift)            // one row a sequence: this thread is the only one that reads or writes its column
-        for (int i = 0; i < taps - 1; i++) st[(size_t)i * channels + ch] = x[i + 1];
 }
 
 template <typename WT>
@@ -188,11 +231,35 @@ MOE_API int moe_seq_conv(int njobs, const float* u0, long long ldu0, const float
     ConvJobs jobs;
     jobs.j[0] = ConvJob{u0, w0, bias0, state0, out32_0, (__nv_bfloat16*)out16_0, ldu0};
     jobs.j[1] = ConvJob{u1, w1, bias1, state1, out32_1, (__nv_bfloat16*)out16_1, ldu1};
-    const int threads = channels >= 256 ? 256 : ((channels + 31) / 32) * 32;
-    const dim3 grid(num_tokens, (channels + threads - 1) / threads, njobs);
+    auto al = [](const void* p, size_t a) { return ((uintptr_t)p % a) == 0; };
+    bool vec = channels % 4 == 0 && state_pitch % 4 == 0;
+    for (int i = 0; i < njobs; i++) {
+        const ConvJob& J = jobs.j[i];
+        vec = vec && J.ldu % 4 == 0 && al(J.u, 16) && al(J.w, 16) && al(J.bias, 16) && al(J.state, 16) && al(J.out32, 16) &&
+              al(J.out16, 8);
+    }
+    const int lanes = vec ? channels / 4 : channels;
+    const int threads = lanes >= 256 ? 256 : ((lanes + 31) / 32) * 32;
+    const int tokb = (vec && num_tokens >= 1024 && taps >= 2 && taps <= 4) ? 4 : 1;
+    const dim3 grid((num_tokens + tokb - 1) / tokb, (lanes + threads - 1) / threads, njobs);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
-    return launch_pdl(seq_conv_kernel, grid, dim3(threads), 0, stream, jobs, taps, channels, state_pitch, seq_of_token,
-                      pos, cu_seqlens, slots, residual, act, shift);
+#define CONV(VEC_, TAPS_, TOKB_)                                                                                            \
+    return launch_pdl(seq_conv_kernel<VEC_, TAPS_, TOKB_>, grid, dim3(threads), 0, stream, jobs, taps, channels, state_pitch, \
+                      seq_of_token, cu_seqlens, slots, num_tokens, residual, act, shift)
+    if (vec && tokb == 4) {
+        if (taps == 2) CONV(true, 2, 4);
+        if (taps == 3) CONV(true, 3, 4);
+        CONV(true, 4, 4);
+    }
+    if (vec) {
+        if (taps == 2) CONV(true, 2, 1);
+        if (taps == 3) CONV(true, 3, 1);
+        if (taps == 4) CONV(true, 4, 1);
+        CONV(true, 0, 1);
+    }
+    if (taps == 4) CONV(false, 4, 1);
+    CONV(false, 0, 1);
+#undef CONV
 }
 
 // table: [vocab, hidden], pair: [buckets + 1, hidden] in table_dt; norm_w: [hidden] 32-bit; x: [T, hidden] 32-bit;

@@ -13,81 +13,148 @@
 
 namespace {
 
-constexpr int SSD_COLS = 32;      // value columns a block
-constexpr int SSD_NP = 8;         // threads that share a column's N rows
+constexpr int SSD_CPT = 4;        // value columns a thread
+constexpr int SSD_CG = 16;        // column groups a block: 64 columns
+constexpr int SSD_COLS = SSD_CPT * SSD_CG;
 constexpr int SSD_TOK = 16;       // tokens staged at a time
 
 __device__ __forceinline__ float softplus32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
-// grid (ceil(dv / 32), heads, sequences), 256 threads: thread (col = tid / 8, kp = tid % 8) holds rows
-// kp, kp + 8, ... of column col of S in registers.
-template <int RPT>
-__global__ void __launch_bounds__(SSD_COLS * SSD_NP)
+// grid (ceil(dv / 64), heads, sequences), KP * 16 threads: thread (kp = tid % KP, cg = tid / KP) holds rows
+// kp * RPT ... kp * RPT + RPT - 1 of four neighbouring columns of S in registers (KP * RPT >= N; rows beyond
+// N stay zero).  A run of SSD_TOK tokens is staged in shared memory as [B | C | the block's columns of x |
+// dt | decay] a token, the next run's loads in flight while this one is worked on; within a run the
+// chain over the tokens has no barrier.
+template <int RPT, int KP>
+__global__ void __launch_bounds__(KP * SSD_CG)
 ssd_scan_kernel(const float* __restrict__ xbc, long long ldx, const float* __restrict__ dt_raw, long long lddt,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ dskip,
                 float* __restrict__ state, long long state_pitch, const int* __restrict__ cu_seqlens,
                 const int* __restrict__ slots, int heads, int groups, int N, int dv, float* __restrict__ y) {
-    extern __shared__ __align__(16) float ssd_smem[];   // per staged token: B[N], C[N], x[32], dt, a
-    const int rowlen = 2 * N + SSD_COLS + 2;
-    const int tid = threadIdx.x, kp = tid & (SSD_NP - 1), cl = tid / SSD_NP;
+    constexpr int NP = RPT * KP, THREADS = KP * SSD_CG;
+    constexpr int PER_TOK = 2 * NP + SSD_COLS + 2;
+    constexpr int ROWLEN = (PER_TOK + 3) & ~3;
+    constexpr int XPT = (PER_TOK + THREADS - 1) / THREADS;
+    __shared__ __align__(16) float sm[SSD_TOK * ROWLEN];
+    const int tid = threadIdx.x, kp = tid % KP, cg = tid / KP;
     const int h = blockIdx.y, s = blockIdx.z, g = h / (heads / groups);
-    const int col = blockIdx.x * SSD_COLS + cl;
+    const int c0 = blockIdx.x * SSD_COLS, col = c0 + cg * SSD_CPT;
     pdl_sync();
     const int tok0 = cu_seqlens[s], cnt = cu_seqlens[s + 1] - tok0;
     if (cnt <= 0) return;
     const int inner = heads * dv;
     float* S = state + (size_t)slots[s] * state_pitch + (size_t)h * N * dv;
-    float sreg[RPT];
+    const bool vec = (dv % 4 == 0) && (((uintptr_t)S) % 16 == 0) && (state_pitch % 4 == 0);
+    float sreg[RPT][SSD_CPT];
 #pragma unroll
     for (int m = 0; m < RPT; m++) {
-        const int n = kp + m * SSD_NP;
-        sreg[m] = (n < N && col < dv) ? S[(size_t)n * dv + col] : 0.f;
+        const int n = kp * RPT + m;
+        if (vec && n < N && col < dv) {
+            const float4 t4 = *reinterpret_cast<const float4*>(S + (size_t)n * dv + col);
+            sreg[m][0] = t4.x, sreg[m][1] = t4.y, sreg[m][2] = t4.z, sreg[m][3] = t4.w;
+        } else {
+#pragma unroll
+            for (int c = 0; c < SSD_CPT; c++) sreg[m][c] = (n < N && col + c < dv) ? S[(size_t)n * dv + col + c] : 0.f;
+        }
     }
     const float bias = dt_bias[h], rate = expf(a_log[h]), skip = dskip[h];
+    const size_t b_at = (size_t)inner + (size_t)g * N, c_at = (size_t)inner + (size_t)groups * N + (size_t)g * N;
+    // What this thread brings into shared memory of every token: elements x = tid, tid + THREADS, ... of
+    // [B | C | the block's columns of x | dt | decay]; where each comes from is worked out once.
+    const float* src[XPT];
+    long long pitch[XPT];
+#pragma unroll
+    for (int e = 0; e < XPT; e++) {
+        const int x = tid + e * THREADS;
+        src[e] = nullptr, pitch[e] = 0;
+        if (x < NP) {
+            if (x < N) src[e] = xbc + (size_t)tok0 * ldx + b_at + x, pitch[e] = ldx;
+        } else if (x < 2 * NP) {
+            if (x - NP < N) src[e] = xbc + (size_t)tok0 * ldx + c_at + (x - NP), pitch[e] = ldx;
+        } else if (x < 2 * NP + SSD_COLS) {
+            const int c = c0 + x - 2 * NP;
+            if (c < dv) src[e] = xbc + (size_t)tok0 * ldx + (size_t)h * dv + c, pitch[e] = ldx;
+        } else if (x < PER_TOK) {
+            src[e] = dt_raw + (size_t)tok0 * lddt + h, pitch[e] = lddt;      // turned into dt or the decay when it is stored
+        }
+    }
+    float ahead[SSD_TOK][XPT];
+    auto fetch = [&](int t0) {
+        const int nt = min(SSD_TOK, cnt - t0);
+#pragma unroll
+        for (int tt = 0; tt < SSD_TOK; tt++) {
+            const long long r = t0 + min(tt, nt - 1);
+#pragma unroll
+            for (int e = 0; e < XPT; e++) ahead[tt][e] = src[e] ? src[e][r * pitch[e]] : 0.f;
+        }
+    };
+    fetch(0);
     for (int t0 = 0; t0 < cnt; t0 += SSD_TOK) {
         const int nt = min(SSD_TOK, cnt - t0);
-        __syncthreads();
-        for (int idx = tid; idx < nt * rowlen; idx += blockDim.x) {
-            const int tt = idx / rowlen, e = idx % rowlen;
-            const size_t r = (size_t)(tok0 + t0 + tt);
-            float v;
-            if (e < N)
-                v = xbc[r * ldx + inner + (size_t)g * N + e];
-            else if (e < 2 * N)
-                v = xbc[r * ldx + inner + (size_t)groups * N + (size_t)g * N + (e - N)];
-            else if (e < 2 * N + SSD_COLS) {
-                const int c = blockIdx.x * SSD_COLS + (e - 2 * N);
-                v = c < dv ? xbc[r * ldx + (size_t)h * dv + c] : 0.f;
-            } else {
-                const float dt = softplus32(dt_raw[r * lddt + h] + bias);
-                v = e == 2 * N + SSD_COLS ? dt : expf(-rate * dt);
-            }
-            ssd_smem[idx] = v;
-        }
-        __syncthreads();
-        for (int tt = 0; tt < nt; tt++) {
-            const float* row = ssd_smem + (size_t)tt * rowlen;
-            const float xv = row[2 * N + cl], dt = row[2 * N + SSD_COLS], a = row[2 * N + SSD_COLS + 1];
-            const float dx = dt * xv;
-            float acc = 0.f;
+        __syncthreads();                     // the run before is no longer read
 #pragma unroll
-            for (int m = 0; m < RPT; m++) {
-                const int n = kp + m * SSD_NP;
-                if (n < N) {
-                    sreg[m] = fmaf(a, sreg[m], row[n] * dx);
-                    acc = fmaf(row[N + n], sreg[m], acc);
+        for (int tt = 0; tt < SSD_TOK; tt++)
+#pragma unroll
+            for (int e = 0; e < XPT; e++) {
+                const int x = tid + e * THREADS;
+                if (x < PER_TOK) {
+                    float val = ahead[tt][e];
+                    if (x >= 2 * NP + SSD_COLS) {
+                        const float dt = softplus32(val + bias);
+                        val = x == 2 * NP + SSD_COLS ? dt : expf(-rate * dt);
+                    }
+                    sm[tt * ROWLEN + x] = val;
                 }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (kp == 0 && col < dv) y[(size_t)(tok0 + t0 + tt) * inner + (size_t)h * dv + col] = fmaf(skip, xv, acc);
+        __syncthreads();
+        if (t0 + SSD_TOK < cnt) fetch(t0 + SSD_TOK);
+#pragma unroll 2
+        for (int tt = 0; tt < nt; tt++) {
+            const float* row = sm + tt * ROWLEN;
+            const float4 x4 = *reinterpret_cast<const float4*>(row + 2 * NP + cg * SSD_CPT);
+            const float dt = row[2 * NP + SSD_COLS], a = row[2 * NP + SSD_COLS + 1];
+            const float xv[SSD_CPT] = {x4.x, x4.y, x4.z, x4.w};
+            const float dx[SSD_CPT] = {dt * x4.x, dt * x4.y, dt * x4.z, dt * x4.w};
+            float acc[2][SSD_CPT] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};      // two chains a column
+#pragma unroll
+            for (int m0 = 0; m0 < RPT; m0 += 4) {
+                const float4 b4 = *reinterpret_cast<const float4*>(row + kp * RPT + m0);
+                const float4 c4 = *reinterpret_cast<const float4*>(row + NP + kp * RPT + m0);
+                const float bi[4] = {b4.x, b4.y, b4.z, b4.w}, ci[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                for (int z = 0; z < 4; z++)
+#pragma unroll
+                    for (int c = 0; c < SSD_CPT; c++) {
+                        sreg[m0 + z][c] = fmaf(a, sreg[m0 + z][c], bi[z] * dx[c]);
+                        acc[z & 1][c] = fmaf(ci[z], sreg[m0 + z][c], acc[z & 1][c]);
+                    }
+            }
+            float sum[SSD_CPT];
+#pragma unroll
+            for (int c = 0; c < SSD_CPT; c++) {
+                sum[c] = acc[0][c] + acc[1][c];
+#pragma unroll
+                for (int off = 1; off < KP; off <<= 1) sum[c] += __shfl_xor_sync(0xffffffffu, sum[c], off);
+            }
+            if (kp == 0) {
+                float* o = y + (size_t)(tok0 + t0 + tt) * inner + (size_t)h * dv + col;
+#pragma unroll
+                for (int c = 0; c < SSD_CPT; c++)
+                    if (col + c < dv) o[c] = fmaf(skip, xv[c], sum[c]);
+            }
         }
     }
 #pragma unroll
     for (int m = 0; m < RPT; m++) {
-        const int n = kp + m * SSD_NP;
-        if (n < N && col < dv) S[(size_t)n * dv + col] = sreg[m];
+        const int n = kp * RPT + m;
+        if (n >= N) continue;
+        if (vec && col < dv) {
+            *reinterpret_cast<float4*>(S + (size_t)n * dv + col) = make_float4(sreg[m][0], sreg[m][1], sreg[m][2], sreg[m][3]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < SSD_CPT; c++)
+                if (col + c < dv) S[(size_t)n * dv + col + c] = sreg[m][c];
+        }
     }
 }
 
@@ -135,14 +202,13 @@ MOE_API int moe_ssd_scan(const float* xbc, long long ldx, const float* dt_raw, l
         state_pitch < (long long)heads * N * dv || heads > 65535 || num_seqs > 65535)
         return (int)cudaErrorInvalidValue;
     const dim3 grid((dv + SSD_COLS - 1) / SSD_COLS, heads, num_seqs);
-    const size_t smem = (size_t)SSD_TOK * (2 * N + SSD_COLS + 2) * sizeof(float);
-#define SCAN(RPT_)                                                                                                  \
-    return launch_pdl(ssd_scan_kernel<RPT_>, grid, dim3(SSD_COLS * SSD_NP), smem, stream, xbc, ldx, dt_raw, lddt,    \
-                      dt_bias, a_log, dskip, state, state_pitch, cu_seqlens, slots, heads, groups, N, dv, y)
-    if (N <= 32) SCAN(4);
-    if (N <= 64) SCAN(8);
-    if (N <= 128) SCAN(16);
-    SCAN(32);
+#define SCAN(RPT_, KP_)                                                                                              \
+    return launch_pdl(ssd_scan_kernel<RPT_, KP_>, grid, dim3(KP_ * SSD_CG), 0, stream, xbc, ldx, dt_raw, lddt, dt_bias, \
+                      a_log, dskip, state, state_pitch, cu_seqlens, slots, heads, groups, N, dv, y)
+    if (N <= 32) SCAN(4, 8);
+    if (N <= 64) SCAN(8, 8);
+    if (N <= 128) SCAN(16, 8);
+    SCAN(16, 16);
 #undef SCAN
 }
 

@@ -17,6 +17,8 @@ from . import build
 DT_F32, DT_BF16 = 0, 1
 # the gate's activation of a gated feed-forward (ACT_* in csrc/common.cuh)
 GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped_sigmoid": 2}
+# what an ungated product's output may pass in the tensor-core kernel's epilogue
+PLAIN_ACTS = {"relu2": 3}
 
 
 class KernelError(RuntimeError):

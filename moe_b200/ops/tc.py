@@ -97,7 +97,8 @@ _workspaces = {}
 def workspace(device) -> Workspace:
     """The scratch of the calling stream: products on the side stream (``Runtime.side_stream``)
     have a workspace of their own, since they may run beside products on the main stream."""
-    side = core._stream() in _side_handles
+    handle = core._stream()
+    side = handle if handle in _side_handles else 0        # every side stream has a workspace of its own
     key = (device.index or 0 if isinstance(device, torch.device) else torch.device(device).index or 0, side)
     if key not in _workspaces:
         _workspaces[key] = Workspace(device)
@@ -131,6 +132,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
             act: str = "silu", act_param: float = 0.0) -> bool:
     """out = x @ w[g].T (PLAIN) or act(x @ gate.T) * (x @ up.T) (SwiGLU, w rows = gate then up; ``act``
     is the gate's activation, one of ``core.GLU_ACTS``, ``act_param`` its constant if it has one).
+
+    Without ``swiglu``, ``act`` may name a function of the output itself (``core.PLAIN_ACTS``: "relu2").
 
     x: [M, K] bf16 (row pitch a multiple of 8); w: [N', K] or [G, N', K] bf16 contiguous;
     out: [M, N] float32 or bfloat16 with N = N' (PLAIN) or N' / 2 (SwiGLU).
@@ -187,7 +190,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, swiglu: bool
                          None if group_offsets is None else group_offsets.data_ptr(), M, bn, splits,
                          None if partials is None else partials.data_ptr(),
                          None if tickets is None else tickets.data_ptr(),
-                         None if status is None else status.data_ptr(), 1 if early_offsets else 0, core.GLU_ACTS[act],
+                         None if status is None else status.data_ptr(), 1 if early_offsets else 0,
+                         core.GLU_ACTS[act] if swiglu else core.PLAIN_ACTS.get(act, 0),
                          float(act_param), core._stream())
     if code == -1:
         return False

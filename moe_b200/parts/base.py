@@ -108,16 +108,19 @@ class Runtime:
     def is_bf16(self) -> bool:
         return self.compute_dtype == torch.bfloat16
 
-    def side_stream(self) -> "torch.cuda.Stream":
-        """A second stream of this runtime, for a branch that may run beside the main one."""
-        if getattr(self, "_side", None) is None:
+    def side_stream(self, index: int = 0) -> "torch.cuda.Stream":
+        """A further stream of this runtime, for a branch that may run beside the main one (``index``
+        tells several apart: a branch that itself forks takes another number)."""
+        if getattr(self, "_sides", None) is None:
+            self._sides = {}
+        if index not in self._sides:
             from ..ops import tc
 
             # (default priority: a higher one was measured slower, the side branch then crowds out
             # the routed experts' first product)
-            self._side = torch.cuda.Stream(device=self.device)
-            tc.register_side_stream(self._side)     # its products get a split-K workspace of their own
-        return self._side
+            self._sides[index] = torch.cuda.Stream(device=self.device)
+            tc.register_side_stream(self._sides[index])     # its products get a split-K workspace of their own
+        return self._sides[index]
 
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.compute_dtype, device=self.device)

@@ -24,6 +24,8 @@ keeps per scheduled run of the layer (``state_request``, handed to ``forward`` a
 """
 from __future__ import annotations
 
+import os
+
 from ..config.spec import LayerSpec
 import torch
 
@@ -113,6 +115,8 @@ class ParallelBlock:
         self.pre1 = make_part("inconv", layer.pre1) if layer.pre1 is not None else None
         self.pre2 = make_part("inconv", layer.pre2) if layer.pre2 is not None else None
         self._ones = None
+        # MOE_B200_FFN_BESIDE=0: a block with two norms runs its feed-forward after its mixer, not beside it
+        self._beside = os.environ.get("MOE_B200_FFN_BESIDE", "1") != "0"
 
     def parts(self):
         return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.scale1, self.scale2, self.pre1, self.pre2)
@@ -147,6 +151,18 @@ class ParallelBlock:
                 raise ValueError("a parallel block with one norm convolves both sublayers' input or neither")
             h, h2 = run_input_convs(rt, [(self.pre1, h, mix32), (self.pre2, h2, ffn32) if self.ffn is not None else None],
                                     batch, block_state)
+        if self.ffn is not None and self.norm2 is not None and self._beside and x.is_cuda:
+            # the two sublayers share nothing but the stream they read: the feed-forward runs on a second
+            # stream beside the mixer (inside a captured step: a fork and a join)
+            main = torch.cuda.current_stream()
+            side = rt.side_stream(2)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                b = self.ffn.forward(rt, h2, batch)
+            a = self.mixer.forward(rt, h, batch, cache_view, state)
+            main.wait_stream(side)
+            b.record_stream(main)
+            return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a), b, self._factor(rt, self.scale2, a))
         a = self.mixer.forward(rt, h, batch, cache_view, state)
         if self.ffn is None:
             return x, ScaledPairDelta(a, self._factor(rt, self.scale1, a))

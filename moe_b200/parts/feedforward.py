@@ -66,6 +66,21 @@ class DenseSwiGLU(Part):
         return linear(rt, swiglu_linear(rt, h.act, self.w_gu, self.activation, self.limit), self.w_down)
 
 
+def relu2_linear(rt, a, w_up, out=None):
+    """relu(a Wu^T)^2 in the compute dtype: in the tensor-core product's epilogue (on the 32-bit
+    accumulator) where that kernel takes the product, else the product's 32-bit output and then the
+    activation."""
+    if out is None:
+        out = torch.empty((a.shape[0], w_up.shape[0]), dtype=rt.compute_dtype, device=a.device)
+    if rt.is_bf16 and a.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16:
+        from ..ops import tc
+
+        if tc.gemm_tc(a, w_up, out, status=rt.status, act="relu2"):
+            return out
+    core.relu2(linear(rt, a, w_up), out)
+    return out
+
+
 class DenseMLP(Part):
     """y = Wd f(Wu n), no gate; ``activation`` names f: "relu2" is relu(z)^2.  The activation is 32-bit
     arithmetic on the first product's 32-bit output; the bfloat16 path rounds its result."""
@@ -96,10 +111,7 @@ class DenseMLP(Part):
         self.w_down = tensors[self.names["down"]].contiguous()
 
     def forward(self, rt, h, batch):
-        z = linear(rt, h.act, self.w_up)
-        act = rt.empty(z.shape)
-        core.relu2(z, act)
-        return linear(rt, act, self.w_down)
+        return linear(rt, relu2_linear(rt, h.act, self.w_up), self.w_down)
 
 
 class CombineDelta(LazyDelta):

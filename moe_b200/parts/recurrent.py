@@ -296,6 +296,7 @@ class SideBySideMixer(Part):
         for side in ("left", "right"):
             sub = p[side]
             self.subs.append((side + ".", make_part("mixer", PartSpec(sub["kind"], dict(sub["params"]), spec.prefix + side + "."))))
+        self.beside = os.environ.get("MOE_B200_SIDE_BY_SIDE_STREAMS", "1") != "0"
         self.graph_safe = all(getattr(m, "graph_safe", False) for _, m in self.subs)
         self.wants32 = any(getattr(m, "wants32", False) for _, m in self.subs)
         if sum(m.kv_request() is not None for _, m in self.subs) > 1:
@@ -352,16 +353,29 @@ class SideBySideMixer(Part):
         self.w_right = tensors[self.names["right_out"]].to(torch.float32).contiguous()
 
     def forward(self, rt, h, batch, cache_view, state):
-        outs, at = [], 0
+        """The right mixer runs on a second stream beside the left one (inside a captured step: a fork
+        and a join); MOE_B200_SIDE_BY_SIDE_STREAMS=0 runs them one after the other."""
+        states, at = [], 0
         for _, m in self.subs:
             r = m.state_request()
-            sub_state = None
-            if r is not None:
-                sub_state = state[:, at:at + r.shape[0]]
-                at += r.shape[0]
-            outs.append(m.forward(rt, h, batch, cache_view if m.kv_request() is not None else None, sub_state))
-        out = torch.empty_like(outs[0])
-        core.pair_norm_mean(outs[0], self.w_left, outs[1], self.w_right, self.eps, out)
+            states.append(state[:, at:at + r.shape[0]] if r is not None else None)
+            at += r.shape[0] if r is not None else 0
+        views = [cache_view if m.kv_request() is not None else None for _, m in self.subs]
+        (_, left), (_, right) = self.subs
+        if self.beside and h.act.is_cuda:
+            main = torch.cuda.current_stream()
+            side = rt.side_stream(1)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                b = right.forward(rt, h, batch, views[1], states[1])
+            a = left.forward(rt, h, batch, views[0], states[0])
+            main.wait_stream(side)
+            b.record_stream(main)
+        else:
+            a = left.forward(rt, h, batch, views[0], states[0])
+            b = right.forward(rt, h, batch, views[1], states[1])
+        out = torch.empty_like(a)
+        core.pair_norm_mean(a, self.w_left, b, self.w_right, self.eps, out)
         return out
 
 
