@@ -58,12 +58,15 @@ whole_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restri
     const float* row = proj + (size_t)t * ld;
     const int nq = nh * d, nk = nkv * d;
     float inv_q = 1.f, inv_k = 1.f;
-    if (q_norm) {
+    const int my_per = (nh + 2 * nkv + gridDim.y - 1) / gridDim.y;
+    const bool has_q = blockIdx.y * my_per < nh;
+    const bool has_k = blockIdx.y * my_per < nh + nkv && (blockIdx.y + 1) * my_per > nh;
+    if (q_norm && has_q) {
         float ss = 0.f;
         for (int e = threadIdx.x; e < nq; e += blockDim.x) ss = fmaf(row[e], row[e], ss);
         inv_q = 1.0f / sqrtf(block_sum(ss, red) / (float)nq + eps);
     }
-    if (k_norm) {
+    if (k_norm && has_k) {
         float ss = 0.f;
         for (int e = threadIdx.x; e < nk; e += blockDim.x) ss = fmaf(row[nq + e], row[nq + e], ss);
         inv_k = 1.0f / sqrtf(block_sum(ss, red) / (float)nk + eps);
@@ -80,8 +83,11 @@ whole_prepare_kernel(const float* __restrict__ proj, int ld, const int* __restri
             append = true;
         }
     }
-    const int total = (nh + 2 * nkv) * D;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    // (few tokens: gridDim.y blocks share a token's head slots, each forming the sums of squares for itself)
+    const int hs_count = nh + 2 * nkv;
+    const int per = (hs_count + gridDim.y - 1) / gridDim.y;
+    const int hs_lo = blockIdx.y * per, hs_hi = min(hs_count, hs_lo + per);
+    for (int idx = hs_lo * D + threadIdx.x; idx < hs_hi * D; idx += blockDim.x) {
         const int hs = idx / D, e = idx % D;
         const bool is_q = hs < nh, is_k = !is_q && hs < nh + nkv;
         const int head = is_q ? hs : is_k ? hs - nh : hs - nh - nkv;
@@ -165,11 +171,14 @@ MOE_API int moe_whole_prepare(const float* proj, int ld, const int* pos, const i
     const WholeCommit c{k_cache, v_cache, seq_end, slots, tables, table_stride, ring, page_size, num_pages};
     const size_t smem = (size_t)(rot + (vfreq ? (dv / 2) * 2 : 0) + 4) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    // from 128 tokens on the blocks fill the GPU anyway; fewer tokens are spread over more blocks
+    const int hs_count = nh + 2 * nkv;
+    const dim3 grid(num_tokens, num_tokens >= 128 ? 1 : min(hs_count, max(1, (hs_count + 3) / 4)));
     if (out_dt == DT_F32)
-        return launch_pdl(whole_prepare_kernel<float>, dim3(num_tokens), WP_THREADS, smem, stream, proj, ld, pos,
+        return launch_pdl(whole_prepare_kernel<float>, grid, WP_THREADS, smem, stream, proj, ld, pos,
                           seq_of_token, q_norm, k_norm, eps, freq, rot, vfreq, nh, nkv, d, dv, D, (float*)q, (float*)k,
                           (float*)v, ldq, ldkv, c, status);
-    return launch_pdl(whole_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), WP_THREADS, smem, stream, proj, ld, pos,
+    return launch_pdl(whole_prepare_kernel<__nv_bfloat16>, grid, WP_THREADS, smem, stream, proj, ld, pos,
                       seq_of_token, q_norm, k_norm, eps, freq, rot, vfreq, nh, nkv, d, dv, D, (__nv_bfloat16*)q,
                       (__nv_bfloat16*)k, (__nv_bfloat16*)v, ldq, ldkv, c, status);
 }

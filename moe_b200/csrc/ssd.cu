@@ -16,16 +16,15 @@ namespace {
 constexpr int SSD_CPT = 4;        // value columns a thread
 constexpr int SSD_CG = 16;        // column groups a block: 64 columns
 constexpr int SSD_COLS = SSD_CPT * SSD_CG;
-constexpr int SSD_TOK = 16;       // tokens staged at a time
 
 __device__ __forceinline__ float softplus32(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // grid (ceil(dv / 64), heads, sequences), KP * 16 threads: thread (kp = tid % KP, cg = tid / KP) holds rows
 // kp * RPT ... kp * RPT + RPT - 1 of four neighbouring columns of S in registers (KP * RPT >= N; rows beyond
 // N stay zero).  A run of SSD_TOK tokens is staged in shared memory as [B | C | the block's columns of x |
-// dt | decay] a token, the next run's loads in flight while this one is worked on; within a run the
-// chain over the tokens has no barrier.
-template <int RPT, int KP>
+// dt | decay] a token (SSD_TOK: tokens staged at a time), the next run's loads in flight while this one is
+// worked on; within a run the chain over the tokens has no barrier.
+template <int RPT, int KP, int SSD_TOK>
 __global__ void __launch_bounds__(KP * SSD_CG)
 ssd_scan_kernel(const float* __restrict__ xbc, long long ldx, const float* __restrict__ dt_raw, long long lddt,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ dskip,
@@ -129,18 +128,24 @@ ssd_scan_kernel(const float* __restrict__ xbc, long long ldx, const float* __res
                         acc[z & 1][c] = fmaf(ci[z], sreg[m0 + z][c], acc[z & 1][c]);
                     }
             }
-            float sum[SSD_CPT];
-#pragma unroll
-            for (int c = 0; c < SSD_CPT; c++) {
-                sum[c] = acc[0][c] + acc[1][c];
-#pragma unroll
-                for (int off = 1; off < KP; off <<= 1) sum[c] += __shfl_xor_sync(0xffffffffu, sum[c], off);
+            // the KP threads of a column group add up their parts; on the way every thread drops the
+            // columns another one carries on (4 shuffles instead of 12): lane bits 0 and 1 of kp say which
+            // column's sum it ends with
+            const bool b0 = (kp & 1) != 0, b1 = (kp & 2) != 0;
+            float v0, v1;
+            {
+                const float p0 = acc[0][0] + acc[1][0], p1 = acc[0][1] + acc[1][1];
+                const float p2 = acc[0][2] + acc[1][2], p3 = acc[0][3] + acc[1][3];
+                v0 = (b0 ? p2 : p0) + __shfl_xor_sync(0xffffffffu, b0 ? p0 : p2, 1);
+                v1 = (b0 ? p3 : p1) + __shfl_xor_sync(0xffffffffu, b0 ? p1 : p3, 1);
             }
-            if (kp == 0) {
-                float* o = y + (size_t)(tok0 + t0 + tt) * inner + (size_t)h * dv + col;
+            v0 = (b1 ? v1 : v0) + __shfl_xor_sync(0xffffffffu, b1 ? v0 : v1, 2);
 #pragma unroll
-                for (int c = 0; c < SSD_CPT; c++)
-                    if (col + c < dv) o[c] = fmaf(skip, xv[c], sum[c]);
+            for (int off = 4; off < KP; off <<= 1) v0 += __shfl_xor_sync(0xffffffffu, v0, off);
+            if (kp < 4) {
+                const int c = (b0 ? 2 : 0) + (b1 ? 1 : 0);
+                const float xc = b0 ? (b1 ? xv[3] : xv[2]) : (b1 ? xv[1] : xv[0]);
+                if (col + c < dv) y[(size_t)(tok0 + t0 + tt) * inner + (size_t)h * dv + col + c] = fmaf(skip, xc, v0);
             }
         }
     }
@@ -198,17 +203,18 @@ MOE_API int moe_ssd_scan(const float* xbc, long long ldx, const float* dt_raw, l
                          float* y, cudaStream_t stream) {
     if (num_seqs <= 0) return 0;
     if (!xbc || !dt_raw || !dt_bias || !a_log || !dskip || !state || !y || heads <= 0 || groups <= 0 || heads % groups ||
-        N <= 0 || N > 256 || dv <= 0 || ldx < (long long)heads * dv + 2LL * groups * N || lddt < heads ||
+        N <= 0 || N > 512 || dv <= 0 || ldx < (long long)heads * dv + 2LL * groups * N || lddt < heads ||
         state_pitch < (long long)heads * N * dv || heads > 65535 || num_seqs > 65535)
         return (int)cudaErrorInvalidValue;
     const dim3 grid((dv + SSD_COLS - 1) / SSD_COLS, heads, num_seqs);
-#define SCAN(RPT_, KP_)                                                                                              \
-    return launch_pdl(ssd_scan_kernel<RPT_, KP_>, grid, dim3(KP_ * SSD_CG), 0, stream, xbc, ldx, dt_raw, lddt, dt_bias, \
+#define SCAN(RPT_, KP_, TOK_)                                                                                        \
+    return launch_pdl(ssd_scan_kernel<RPT_, KP_, TOK_>, grid, dim3(KP_ * SSD_CG), 0, stream, xbc, ldx, dt_raw, lddt, dt_bias, \
                       a_log, dskip, state, state_pitch, cu_seqlens, slots, heads, groups, N, dv, y)
-    if (N <= 32) SCAN(4, 8);
-    if (N <= 64) SCAN(8, 8);
-    if (N <= 128) SCAN(16, 8);
-    SCAN(16, 16);
+    if (N <= 32) SCAN(4, 8, 16);
+    if (N <= 64) SCAN(8, 8, 16);
+    if (N <= 128) SCAN(16, 8, 16);
+    if (N <= 256) SCAN(16, 16, 16);
+    SCAN(32, 16, 8);
 #undef SCAN
 }
 

@@ -193,8 +193,8 @@ class SSDMixer(Part):
         self.channels = self.inner + 2 * self.groups * self.n
         if self.nh % self.groups or self.inner % self.norm_groups:
             raise ValueError("ssd: heads must be a multiple of groups, and heads * value_dim of norm_groups")
-        if not (0 < self.n <= 256 and 1 <= self.taps <= 16):
-            raise ValueError(f"ssd: state of {self.n}, {self.taps} taps; the kernels take up to 256 and 1 to 16")
+        if not (0 < self.n <= 512 and 1 <= self.taps <= 16):
+            raise ValueError(f"ssd: state of {self.n}, {self.taps} taps; the kernels take up to 512 and 1 to 16")
 
     def tensors(self):
         n = self.names

@@ -381,7 +381,7 @@ def test_a_key_that_towers_is_seen_exactly_where_the_chunk_says(where, decode):
 
 
 @pytest.mark.parametrize("heads,groups,n,dv,ng", [(4, 2, 24, 16, 2), (2, 1, 16, 32, 1), (1, 1, 8, 40, 1), (3, 3, 40, 8, 3),
-                                                  (2, 1, 64, 64, 2), (2, 2, 130, 48, 4)])
+                                                  (2, 1, 64, 64, 2), (2, 2, 130, 48, 4), (1, 1, 300, 16, 1)])
 @pytest.mark.parametrize("bf16", [False, True])
 def test_state_space_recurrence_and_gated_norm_over_steps(heads, groups, n, dv, ng, bf16):
     from moe_b200.ops import core
@@ -634,6 +634,31 @@ def test_the_trace_program_replays_a_mixed_schedule(root, dtype, tmp_path):
     tol = tol_of("mix", dtype) * float(ra.abs().max())
     assert float((got0 - torch.stack([ra[0], ra[69], rb[24]])).abs().max()) < tol
     assert float((got6[0] - ra[79]).abs().max()) < tol
+
+
+def test_command_line_generates_and_traces_the_table_s_picks(root, tmp_path):
+    import moe_b200
+
+    d = U.model_folder(root, "mix")
+    cfg, w = model_of(d)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    run = lambda *a: subprocess.run([sys.executable, os.path.join(ROOT, "bin", "moe"), *a], capture_output=True, text=True,
+                                    env=env, timeout=900)
+    tr = tmp_path / "routes.jsonl"
+    r = run("run", d, "--ids", "5,17,3,9", "-n", "6", "--no-stream", "--dtype", "float32", "--trace", str(tr))
+    assert r.returncode == 0, r.stderr[-2000:]
+    toks = json.loads(r.stdout.strip().splitlines()[-1])
+    _, eng = engine_of(root, "mix", "float32")
+    assert moe_b200.generate(eng, [[5, 17, 3, 9]], max_tokens=6)[0].tokens == toks
+    recs = [json.loads(x) for x in tr.read_text().splitlines()]
+    fed = [5, 17, 3, 9] + toks[:-1]
+    routed = [i for i, L in enumerate(cfg["layers"]) if L["mlp"] and L["mlp"]["kind"] == "moe"]
+    assert len(recs) == 1 + len(fed) * len(routed)
+    for x in recs[1:]:
+        table = w[f"l{x['layer']}.mlp.table"]
+        top = table.shape[1]
+        assert [e for e, _ in x["experts"]] == table[fed[x["pos"]]].tolist()
+        assert all(abs(wt - 1.0 / top) < 1e-6 for _, wt in x["experts"])
 
 
 def test_the_summary_names_the_design_s_parts(root):
