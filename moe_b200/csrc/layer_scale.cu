@@ -4,6 +4,7 @@
 //   v = x[r] + a[r] * sa + b[r] * sb      (b and sb may be null: one sublayer)
 //   if write_back: x[r] = v               (the 32-bit residual stream)
 //   y = v / sqrt(mean(v^2) + eps) * w;  out32[i] = y;  out16[i] = bf16(y)
+//   with w2: out32b[i] = v / sqrt(mean(v^2) + eps) * w2, a second norm of the same row (one statistic)
 // b may still be the uncombined output of routed experts (ScaledCombine),
 //   b[t] = sum_j w[t, j] * y[pos[t, j]] + shared[t],
 // added up here in the order of moe_combine_kernel in moe.cu, which spares that launch and a pass.
@@ -38,7 +39,8 @@ __global__ void __launch_bounds__(512)
 rmsnorm_scaled_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ sa,
                       const float* __restrict__ b, const float* __restrict__ sb, const float* __restrict__ w,
                       const int* __restrict__ rows, float* __restrict__ out32, __nv_bfloat16* __restrict__ out16,
-                      int hidden, float eps, int write_back, int num_src_rows, int* status, const ScaledCombine cs) {
+                      int hidden, float eps, int write_back, int num_src_rows, int* status, const ScaledCombine cs,
+                      const float* __restrict__ w2, float* __restrict__ out32b) {
     extern __shared__ __align__(16) float row[];
     __shared__ float red[32];
     const int i = blockIdx.x;
@@ -106,6 +108,11 @@ rmsnorm_scaled_kernel(float* __restrict__ x, const float* __restrict__ a, const 
                 u.x = *reinterpret_cast<unsigned*>(&lo), u.y = *reinterpret_cast<unsigned*>(&hi);
                 reinterpret_cast<uint2*>(out16 + (size_t)i * hidden)[j] = u;
             }
+            if (w2) {       // a second norm of the same row: the same statistic, another weight
+                const float4 g2 = reinterpret_cast<const float4*>(w2)[j];
+                reinterpret_cast<float4*>(out32b + (size_t)i * hidden)[j] =
+                    make_float4(v.x * scale * g2.x, v.y * scale * g2.y, v.z * scale * g2.z, v.w * scale * g2.w);
+            }
         }
         return;
     }
@@ -113,6 +120,7 @@ rmsnorm_scaled_kernel(float* __restrict__ x, const float* __restrict__ a, const 
         const float y = row[j] * scale * w[j];
         if (out32) out32[(size_t)i * hidden + j] = y;
         if (out16) out16[(size_t)i * hidden + j] = __float2bfloat16_rn(y);
+        if (w2) out32b[(size_t)i * hidden + j] = row[j] * scale * w2[j];
     }
 }
 
@@ -122,9 +130,10 @@ MOE_API int moe_rmsnorm_scaled(float* x, const float* a, const float* sa, const 
                                const float* w, const int* rows, float* out32, void* out16, int num_out_rows,
                                int num_src_rows, int hidden, float eps, int write_back, int* status,
                                const float* cy, const int* cpos, const float* cw, int top_k, const float* cshared,
-                               cudaStream_t stream) {
+                               const float* w2, float* out32b, cudaStream_t stream) {
     if (num_out_rows <= 0) return 0;
-    if (!x || !a || !sa || !w || ((b || cy) && !sb) || (b && cy) || (cy && (!cpos || !cw || top_k <= 0)) || hidden <= 0)
+    if (!x || !a || !sa || !w || ((b || cy) && !sb) || (b && cy) || (cy && (!cpos || !cw || top_k <= 0)) || hidden <= 0 ||
+        (w2 && !out32b))
         return (int)cudaErrorInvalidValue;
     const ScaledCombine cs{cy, cpos, cw, top_k, cshared};
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
@@ -132,7 +141,7 @@ MOE_API int moe_rmsnorm_scaled(float* x, const float* a, const float* sa, const 
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto al = [](const void* p, size_t n) { return ((uintptr_t)p % n) == 0; };
     const bool vec = hidden % 4 == 0 && al(x, 16) && al(a, 16) && al(sa, 16) && al(b, 16) && al(sb, 16) && al(w, 16) &&
-                     al(out32, 16) && al(out16, 8) && al(cy, 16) && al(cshared, 16);
+                     al(out32, 16) && al(out16, 8) && al(cy, 16) && al(cshared, 16) && al(w2, 16) && al(out32b, 16);
     if (smem > 48 * 1024) {
         const cudaError_t e = vec ? cudaFuncSetAttribute(rmsnorm_scaled_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
                                   : cudaFuncSetAttribute(rmsnorm_scaled_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -140,7 +149,7 @@ MOE_API int moe_rmsnorm_scaled(float* x, const float* a, const float* sa, const 
     }
     if (vec)
         return launch_pdl(rmsnorm_scaled_kernel<true>, dim3(num_out_rows), threads, smem, stream, x, a, sa, b, sb, w, rows,
-                          out32, (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status, cs);
+                          out32, (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status, cs, w2, out32b);
     return launch_pdl(rmsnorm_scaled_kernel<false>, dim3(num_out_rows), threads, smem, stream, x, a, sa, b, sb, w, rows,
-                      out32, (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status, cs);
+                      out32, (__nv_bfloat16*)out16, hidden, eps, write_back, num_src_rows, status, cs, w2, out32b);
 }

@@ -12,7 +12,8 @@
 //                   a step's first row is the sequence's state, which the block of that row then
 //                   replaces by the step's last token (it is the state's only reader).
 //   pair_norm_mean  out = (rmsnorm(a) * wa + rmsnorm(b) * wb) / 2, both norms over the model's width.
-//   act_rows        out = f(in) element by element, rounded to the activation dtype (f: relu(x)^2).
+//   relu2           out = relu(in)^2 element by element, rounded to the activation dtype (where the
+//                   tensor-core product's epilogue does not form it).
 //   table_route     a token's experts are row `token id` of an integer table; each weighs 1 / top.
 // All arithmetic is 32-bit; only stores into activation buffers round.
 #include "common.cuh"

@@ -64,7 +64,7 @@ def lib():
             "moe_wkv_decay": [P, P, P, I, I, I, P, P],
             "moe_wkv_scan": [P, P, P, P, LL, P, P, LL, P, P, I, I, I, P, P],
             "moe_wkv_finish": [P, P, LL, P, F, P, I, I, I, P, I, P],
-            "moe_rmsnorm_scaled": [P, P, P, P, P, P, P, P, P, I, I, I, F, I, P, P, P, P, I, P, P],
+            "moe_rmsnorm_scaled": [P, P, P, P, P, P, P, P, P, I, I, I, F, I, P, P, P, P, I, P, P, P, P],
             "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
             "moe_norm_route": [P, P, P, F, I, I, P, P, P, P, I, I, I, I, F, P, P, P, P, P, P, P, P, P, P, I, I, P],
             "moe_align": [P, I, I, I, P, P, P, P, P],
@@ -564,11 +564,13 @@ def wkv_finish(o, gate, norm_w, eps, batch, out, *, heads, d):
 
 
 def rmsnorm_scaled(x, a, sa, b, sb, weight, eps, *, rows=None, out32=None, out16=None, write_back=True, status=None,
-                   combine=None):
+                   combine=None, second=None):
     """y = rmsnorm(x[r] + a[r] * sa + b[r] * sb) with per-channel scales sa, sb (``b``, ``sb`` may be
     None); with ``write_back`` (and no ``rows``) the sum is stored back into ``x``.  Instead of ``b``,
     ``combine`` may bring routed experts' outputs before their combine (y, pos_of_pair, topk_w, top_k,
-    shared; no gate on the shared expert): b[t] = sum_j w[t, j] y[pos[t, j]] + shared[t] is formed here."""
+    shared; no gate on the shared expert): b[t] = sum_j w[t, j] y[pos[t, j]] + shared[t] is formed here.
+    ``second=(weight2, out32b)``: a second RMS norm of the same rows with another weight (the statistic is
+    the same), into a float32 tensor of its own."""
     _chk(x, "x", torch.float32, 2), _chk(weight, "weight", torch.float32, 1)
     _chk(a, "a", torch.float32, 2), _chk(sa, "sa", torch.float32, 1)
     S, H = x.shape
@@ -598,9 +600,15 @@ def rmsnorm_scaled(x, a, sa, b, sb, weight, eps, *, rows=None, out32=None, out16
             _chk(cshared, "shared", torch.float32, 2)
             if cshared.shape != x.shape:
                 raise KernelError("rmsnorm_scaled: the shared expert's output")
+    w2 = o2 = None
+    if second is not None:
+        w2, o2 = second
+        _chk(w2, "second weight", torch.float32, 1), _chk(o2, "second output", torch.float32, 2)
+        if w2.numel() != H or o2.shape[0] < n_out or o2.shape[1] != H:
+            raise KernelError("rmsnorm_scaled: the second norm's weight or output")
     _ok(lib().moe_rmsnorm_scaled(_p(x), _p(a), _p(sa), _p(b), _p(sb), _p(weight), _p(rows), _p(out32), _p(out16), n_out,
                                  S, H, float(eps), 1 if (write_back and rows is None) else 0, _p(status), _p(cy), _p(cpos),
-                                 _p(cw), int(top_k), _p(cshared), _stream()),
+                                 _p(cw), int(top_k), _p(cshared), _p(w2), _p(o2), _stream()),
         "rmsnorm_scaled")
 
 

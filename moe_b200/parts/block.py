@@ -142,10 +142,18 @@ class ParallelBlock:
         mix32 = getattr(self.mixer, "wants32", False)
         ffn32 = getattr(self.ffn, "wants32", False)
         convs = self.pre1 is not None or self.pre2 is not None
-        h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt),
-                               want32=mix32 or (ffn32 and self.norm2 is None) or convs)
-        # (norm1 has written the sum back: a second norm reads the same x, with nothing pending)
-        h2 = self.norm2.forward(rt, x, want32=ffn32 or convs) if self.norm2 is not None else h
+        both = None
+        if convs and self.norm2 is not None and self.pre1 is not None and self.pre2 is not None:
+            # two norms of the same x whose outputs only the convolutions read: one kernel, one statistic
+            pair = getattr(self.norm1, "forward_pair", None)
+            both = pair(rt, x, delta_for(self.norm1, pending, rt), self.norm2) if pair is not None else None
+        if both is not None:
+            h, h2 = both
+        else:
+            h = self.norm1.forward(rt, x, delta=delta_for(self.norm1, pending, rt),
+                                   want32=mix32 or (ffn32 and self.norm2 is None) or convs)
+            # (norm1 has written the sum back: a second norm reads the same x, with nothing pending)
+            h2 = self.norm2.forward(rt, x, want32=ffn32 or convs) if self.norm2 is not None else h
         if convs:
             if self.norm2 is None and self.ffn is not None and (self.pre1 is None) != (self.pre2 is None):
                 raise ValueError("a parallel block with one norm convolves both sublayers' input or neither")

@@ -47,6 +47,24 @@ class RMSNorm(Part):
         core.rmsnorm(t, self.weight, self.eps, out32=out, write_back=False, status=rt.status)
         return out
 
+    def forward_pair(self, rt, x, delta, other):
+        """This norm and ``other`` (an RMS norm of the same size and eps with a weight of its own) of the
+        same x + delta in one kernel with one statistic: (Activations, Activations), both 32-bit only, or
+        None where that is not possible (the caller then runs the two norms one after the other)."""
+        if (not isinstance(other, RMSNorm) or other.eps != self.eps or other.size != self.size
+                or not isinstance(delta, LazyDelta) or delta.kind != "scaled_pair"):
+            return None
+        b, combine = delta.b, None
+        if isinstance(b, LazyDelta):
+            if b.kind == "expert_combine" and b.shared_gate is None:
+                b, combine = None, (b.y, b.pos_of_pair, b.topk_w, b.top_k, b.shared)
+            else:
+                b = b.materialize(rt)
+        o1, o2 = rt.empty(x.shape, torch.float32), rt.empty(x.shape, torch.float32)
+        core.rmsnorm_scaled(x, delta.a, delta.sa, b, delta.sb, self.weight, self.eps, out32=o1, write_back=True,
+                            status=rt.status, combine=combine, second=(other.weight, o2))
+        return Activations(act=o1, f32=o1), Activations(act=o2, f32=o2)
+
     def forward(self, rt, x, delta=None, rows=None, want32=False, write_back=True) -> Activations:
         """Normalise ``x (+ delta)``; with ``delta`` the sum is written back into ``x``
         (unless ``rows`` selects a subset, which leaves ``x`` alone)."""

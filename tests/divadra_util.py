@@ -73,7 +73,7 @@ CONFIGS = {
         layer(parallel(left(4, 1, 32, 32, chunk=130, rot=32, scale=1.5), 2, 32), dense(64))]),
     # heads of 128 and 64 (records the tensor-core kernels take), a wider model, chunks of several pages,
     # a state of 64 by 64
-    "wide": dict(vocab=203, width=128, eps=1e-5, taps=4, buckets=211, mul_prev=31, mul_cur=37, rank=8, layers=[
+    "wide": dict(vocab=203, width=128, eps=1e-5, taps=4, buckets=211, mul_prev=41, mul_cur=37, rank=8, layers=[
         layer(parallel(left(2, 1, 128, 64, chunk=150, rot=64, base=250.0, scale=0.09), 2, 64), moe(4, 2, 64)),
         layer(mamba2(2, 64, 64, 1, 2, 4), dense(160)),
         layer(parallel(left(4, 4, 64, 64, chunk=None, rot=32, scale=0.125), 1, 64), None)]),

@@ -181,7 +181,7 @@ def test_causal_convolution_over_steps_with_state(width, taps, residual, act):
     assert float(state[:, :7].abs().max()) == 0.0          # what lies before the offset is someone else's
 
 
-@pytest.mark.parametrize("vocab,width,buckets,mp,mc", [(50, 64, 7, 3, 5), (33, 40, 1, 1, 1), (70000, 32, 509, 40503, 65599)])
+@pytest.mark.parametrize("vocab,width,buckets,mp,mc", [(50, 64, 7, 3, 5), (33, 40, 1, 1, 1), (70000, 32, 521, 40503, 65599)])
 def test_pair_embedding_takes_the_previous_token_from_the_step_or_the_state(vocab, width, buckets, mp, mc):
     from moe_b200.ops import core
 
