@@ -983,8 +983,14 @@ def divadra_kernels(sh, pk):
     y = torch.empty((T, inner), device=dev)
     off = (sh["conv"] - 1) * ch
     ms = _median_ms(lambda: core.ssd_scan(xbc, pin[:, inner + ch:], dtb, alog, dsk, sstate, batch, y, heads=sheads, groups=G_, n=N,
-                                          dv=sdv, offset=off))
+                                          dv=sdv, offset=off, segments=1))
     row("ssd_scan (4 sequences of 2,048 tokens)", ms, T * (ch + inner) * 4, flops=4.0 * T * inner * N)
+    # one sequence alone: the chain over its tokens, and the same cut into segments that run side by side
+    b1 = G.make_batch(dev, [1], [0], [n])
+    for label, segs in (("in one chain", 1), ("in 8 segments side by side", 8)):
+        row(f"ssd_scan (one sequence of 2,048 tokens, {label})", _median_ms(lambda: core.ssd_scan(
+            xbc[:n], pin[:n, inner + ch:], dtb, alog, dsk, sstate, b1, y[:n], heads=sheads, groups=G_, n=N, dv=sdv, offset=off,
+            segments=segs)), n * (ch + inner) * 4)
     out["ssd_scan (4 sequences of 2,048 tokens)"]["us_per_token_of_a_sequence"] = round(ms * 1e3 / n, 3)
     st64 = torch.zeros((66, off + sheads * N * sdv), device=dev)
     x1, p1, y1 = r(64, ch), r(64, 2 * inner + 2 * G_ * N + sheads), torch.empty((64, inner), device=dev)
@@ -1000,8 +1006,11 @@ def divadra_kernels(sh, pk):
     rr, kk2, vv2, decay = r(T, I) / 8, r(T, I) / 8, r(T, I), torch.rand(T, I, device=dev)
     o, u = torch.empty((T, I), device=dev), r(wh, wd)
     wstate = torch.zeros((B + 2, H + I * wd), device=dev)
-    ms = _median_ms(lambda: core.wkv_scan(rr, kk2, vv2, decay, u, wstate[:, H:], batch, o, heads=wh, d=wd))
+    ms = _median_ms(lambda: core.wkv_scan(rr, kk2, vv2, decay, u, wstate[:, H:], batch, o, heads=wh, d=wd, segments=1))
     row("wkv_scan (the recurrent mixer's, 4 sequences of 2,048 tokens)", ms, T * I * 4 * 5, flops=6.0 * T * I * wd)
+    for label, segs in (("in one chain", 1), ("in 8 segments side by side", 8)):
+        row(f"wkv_scan (one sequence of 2,048 tokens, {label})", _median_ms(lambda: core.wkv_scan(
+            rr[:n], kk2[:n], vv2[:n], decay[:n], u, wstate[:, H:], b1, o[:n], heads=wh, d=wd, segments=segs)), n * I * 4 * 5)
     out["wkv_scan (the recurrent mixer's, 4 sequences of 2,048 tokens)"]["us_per_token_of_a_sequence"] = round(ms * 1e3 / n, 3)
     st64w = torch.zeros((66, H + I * wd), device=dev)
     r1 = lambda: (r(64, I) / 8)

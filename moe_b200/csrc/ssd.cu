@@ -8,6 +8,15 @@
 //               block of the input projection.
 //   ssd_finish  y * silu(z), then an RMS norm over each of `norm_groups` equal parts of the row
 //               (x / sqrt(mean(x^2) + eps) * w), rounded to the activation dtype.
+//               Few, long sequences leave most SMs idle and the chain over the tokens long, so a sequence's
+//               tokens may be cut into `segs` segments that run side by side (the decay is one number a
+//               head and step, so a segment's effect on what follows is its own end state from a zero
+//               start, E, and the product of its decays, A):
+//                 phase 1  every segment but a sequence's last: E and A into a workspace, no outputs
+//                 phase 2  every segment: its start state S <- A_q S + E_q over the segments q before it,
+//                          begun from the sequence's state, then the recurrence with outputs; the last
+//                          segment that holds tokens writes the state back
+//               which changes the order of additions, nothing else.
 // Everything is 32-bit arithmetic; the state never leaves 32 bits.
 #include "common.cuh"
 
@@ -24,38 +33,70 @@ __device__ __forceinline__ float softplus32(float z) { return z > 20.f ? z : log
 // N stay zero).  A run of SSD_TOK tokens is staged in shared memory as [B | C | the block's columns of x |
 // dt | decay] a token (SSD_TOK: tokens staged at a time), the next run's loads in flight while this one is
 // worked on; within a run the chain over the tokens has no barrier.
-template <int RPT, int KP, int SSD_TOK>
+struct SsdSegments {
+    int segs;          // segments a sequence (1: none of this)
+    int seg_len;       // tokens a segment (a multiple of the staged run)
+    int phase;         // 0: the whole sequence in one go; 1, 2: see the head of this file
+    float* ends;       // [sequence][segment][head][N][dv]: a segment's end state from a zero start
+    float* decays;     // [sequence][segment][head]: the product of its decays
+};
+
+// PHASE (of SsdSegments) is known when compiled, so that the plain chain carries nothing of the other two.
+template <int RPT, int KP, int SSD_TOK, int PHASE>
 __global__ void __launch_bounds__(KP * SSD_CG)
 ssd_scan_kernel(const float* __restrict__ xbc, long long ldx, const float* __restrict__ dt_raw, long long lddt,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ dskip,
                 float* __restrict__ state, long long state_pitch, const int* __restrict__ cu_seqlens,
-                const int* __restrict__ slots, int heads, int groups, int N, int dv, float* __restrict__ y) {
+                const int* __restrict__ slots, int heads, int groups, int N, int dv, float* __restrict__ y,
+                const SsdSegments sg) {
     constexpr int NP = RPT * KP, THREADS = KP * SSD_CG;
     constexpr int PER_TOK = 2 * NP + SSD_COLS + 2;
     constexpr int ROWLEN = (PER_TOK + 3) & ~3;
     constexpr int XPT = (PER_TOK + THREADS - 1) / THREADS;
     __shared__ __align__(16) float sm[SSD_TOK * ROWLEN];
     const int tid = threadIdx.x, kp = tid % KP, cg = tid / KP;
-    const int h = blockIdx.y, s = blockIdx.z, g = h / (heads / groups);
+    const int h = blockIdx.y, s = blockIdx.z / sg.segs, seg = blockIdx.z % sg.segs, g = h / (heads / groups);
     const int c0 = blockIdx.x * SSD_COLS, col = c0 + cg * SSD_CPT;
     pdl_sync();
-    const int tok0 = cu_seqlens[s], cnt = cu_seqlens[s + 1] - tok0;
+    const int seq_tok0 = cu_seqlens[s], seq_cnt = cu_seqlens[s + 1] - seq_tok0;
+    // this block's tokens: the sequence's, or one segment of them
+    const int tok0 = seq_tok0 + seg * sg.seg_len;
+    const int cnt = sg.segs > 1 ? min(sg.seg_len, seq_cnt - seg * sg.seg_len) : seq_cnt;
     if (cnt <= 0) return;
+    const bool last_seg = sg.segs == 1 || (seg + 1) * sg.seg_len >= seq_cnt;       // the last one that holds tokens
+    if (PHASE == 1 && last_seg) return;                                         // nothing comes after it
     const int inner = heads * dv;
     float* S = state + (size_t)slots[s] * state_pitch + (size_t)h * N * dv;
-    const bool vec = (dv % 4 == 0) && (((uintptr_t)S) % 16 == 0) && (state_pitch % 4 == 0);
+    const size_t plane = (size_t)N * dv;
+    float* ends = sg.ends ? sg.ends + ((size_t)s * sg.segs * heads + h) * plane : nullptr;      // + segment * heads * plane
+    float* decays = sg.decays ? sg.decays + (size_t)s * sg.segs * heads + h : nullptr;           // + segment * heads
+    const bool vec = (dv % 4 == 0) && (((uintptr_t)S) % 16 == 0) && (state_pitch % 4 == 0) && (((uintptr_t)sg.ends) % 16 == 0);
     float sreg[RPT][SSD_CPT];
 #pragma unroll
     for (int m = 0; m < RPT; m++) {
         const int n = kp * RPT + m;
-        if (vec && n < N && col < dv) {
+        if (PHASE != 1 && vec && n < N && col < dv) {
             const float4 t4 = *reinterpret_cast<const float4*>(S + (size_t)n * dv + col);
             sreg[m][0] = t4.x, sreg[m][1] = t4.y, sreg[m][2] = t4.z, sreg[m][3] = t4.w;
         } else {
 #pragma unroll
-            for (int c = 0; c < SSD_CPT; c++) sreg[m][c] = (n < N && col + c < dv) ? S[(size_t)n * dv + col + c] : 0.f;
+            for (int c = 0; c < SSD_CPT; c++)
+                sreg[m][c] = (PHASE != 1 && n < N && col + c < dv) ? S[(size_t)n * dv + col + c] : 0.f;
         }
     }
+    if (PHASE == 2)       // the segments before this one, in order: S <- A_q S + E_q
+        for (int q = 0; q < seg; q++) {
+            const float aq = decays[(size_t)q * heads];
+            const float* eq = ends + (size_t)q * heads * plane;
+#pragma unroll
+            for (int m = 0; m < RPT; m++) {
+                const int n = kp * RPT + m;
+#pragma unroll
+                for (int c = 0; c < SSD_CPT; c++)
+                    if (n < N && col + c < dv) sreg[m][c] = fmaf(aq, sreg[m][c], eq[(size_t)n * dv + col + c]);
+            }
+        }
+    float decay_product = 1.f;
     const float bias = dt_bias[h], rate = expf(a_log[h]), skip = dskip[h];
     const size_t b_at = (size_t)inner + (size_t)g * N, c_at = (size_t)inner + (size_t)groups * N + (size_t)g * N;
     // What this thread brings into shared memory of every token: elements x = tid, tid + THREADS, ... of
@@ -114,6 +155,16 @@ ssd_scan_kernel(const float* __restrict__ xbc, long long ldx, const float* __res
             const float dt = row[2 * NP + SSD_COLS], a = row[2 * NP + SSD_COLS + 1];
             const float xv[SSD_CPT] = {x4.x, x4.y, x4.z, x4.w};
             const float dx[SSD_CPT] = {dt * x4.x, dt * x4.y, dt * x4.z, dt * x4.w};
+            if (PHASE == 1) {         // the end state and the decays' product alone
+                decay_product *= a;
+#pragma unroll
+                for (int m = 0; m < RPT; m++) {
+                    const float bm = row[kp * RPT + m];
+#pragma unroll
+                    for (int c = 0; c < SSD_CPT; c++) sreg[m][c] = fmaf(a, sreg[m][c], bm * dx[c]);
+                }
+                continue;
+            }
             float acc[2][SSD_CPT] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};      // two chains a column
 #pragma unroll
             for (int m0 = 0; m0 < RPT; m0 += 4) {
@@ -148,6 +199,11 @@ ssd_scan_kernel(const float* __restrict__ xbc, long long ldx, const float* __res
                 if (col + c < dv) y[(size_t)(tok0 + t0 + tt) * inner + (size_t)h * dv + col + c] = fmaf(skip, xc, v0);
             }
         }
+    }
+    if (PHASE == 2 && !last_seg) return;          // only the sequence's last segment leaves the state behind
+    if (PHASE == 1) {
+        S = ends + (size_t)seg * heads * plane;
+        if (tid == 0) decays[(size_t)seg * heads] = decay_product;
     }
 #pragma unroll
     for (int m = 0; m < RPT; m++) {
@@ -200,22 +256,38 @@ ssd_finish_kernel(const float* __restrict__ y, const float* __restrict__ z, long
 MOE_API int moe_ssd_scan(const float* xbc, long long ldx, const float* dt_raw, long long lddt, const float* dt_bias,
                          const float* a_log, const float* dskip, float* state, long long state_pitch,
                          const int* cu_seqlens, const int* slots, int num_seqs, int heads, int groups, int N, int dv,
-                         float* y, cudaStream_t stream) {
+                         float* y, int segs, int seg_len, float* ends, float* decays, cudaStream_t stream) {
     if (num_seqs <= 0) return 0;
     if (!xbc || !dt_raw || !dt_bias || !a_log || !dskip || !state || !y || heads <= 0 || groups <= 0 || heads % groups ||
         N <= 0 || N > 512 || dv <= 0 || ldx < (long long)heads * dv + 2LL * groups * N || lddt < heads ||
         state_pitch < (long long)heads * N * dv || heads > 65535 || num_seqs > 65535)
         return (int)cudaErrorInvalidValue;
-    const dim3 grid((dv + SSD_COLS - 1) / SSD_COLS, heads, num_seqs);
-#define SCAN(RPT_, KP_, TOK_)                                                                                        \
-    return launch_pdl(ssd_scan_kernel<RPT_, KP_, TOK_>, grid, dim3(KP_ * SSD_CG), 0, stream, xbc, ldx, dt_raw, lddt, dt_bias, \
-                      a_log, dskip, state, state_pitch, cu_seqlens, slots, heads, groups, N, dv, y)
-    if (N <= 32) SCAN(4, 8, 16);
-    if (N <= 64) SCAN(8, 8, 16);
-    if (N <= 128) SCAN(16, 8, 16);
-    if (N <= 256) SCAN(16, 16, 16);
-    SCAN(32, 16, 8);
+    if (segs < 1 || (segs > 1 && (!ends || !decays || seg_len <= 0 || seg_len % 16 || (long long)num_seqs * segs > 65535)))
+        return (int)cudaErrorInvalidValue;
+    const dim3 grid((dv + SSD_COLS - 1) / SSD_COLS, heads, num_seqs * segs);
+    // one launch, or phase 1 and then phase 2 of the segmented form
+    for (int phase = segs > 1 ? 1 : 0; phase <= (segs > 1 ? 2 : 0); phase++) {
+        const SsdSegments sg{segs, seg_len, phase, ends, decays};
+        int code;
+#define SCAN_P(RPT_, KP_, TOK_, PH_)                                                                                    \
+    code = launch_pdl(ssd_scan_kernel<RPT_, KP_, TOK_, PH_>, grid, dim3(KP_ * SSD_CG), 0, stream, xbc, ldx, dt_raw, lddt,    \
+                      dt_bias, a_log, dskip, state, state_pitch, cu_seqlens, slots, heads, groups, N, dv, y, sg)
+#define SCAN(RPT_, KP_, TOK_)                                                                                          \
+    do {                                                                                                               \
+        if (phase == 0) SCAN_P(RPT_, KP_, TOK_, 0);                                                                    \
+        else if (phase == 1) SCAN_P(RPT_, KP_, TOK_, 1);                                                               \
+        else SCAN_P(RPT_, KP_, TOK_, 2);                                                                               \
+    } while (0)
+        if (N <= 32) SCAN(4, 8, 16);
+        else if (N <= 64) SCAN(8, 8, 16);
+        else if (N <= 128) SCAN(16, 8, 16);
+        else if (N <= 256) SCAN(16, 16, 16);
+        else SCAN(32, 16, 8);
 #undef SCAN
+#undef SCAN_P
+        if (code) return code;
+    }
+    return 0;
 }
 
 // y: [T, inner] 32-bit; z: the gate's columns of the input projection, row pitch ldz; norm_w: [inner];

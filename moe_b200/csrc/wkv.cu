@@ -143,6 +143,23 @@ wkv_decay_kernel(const float* __restrict__ low, const float* __restrict__ w2t, c
     }
 }
 
+// Few, long sequences leave most SMs idle and the chain over the tokens long, so a sequence's tokens may
+// be cut into `segs` segments that run side by side.  The decay acts on a row of the state at a time, so a
+// segment's effect on what follows is its own end state from a zero start, E [d][d], and the product of
+// its decays per row, A [d]:
+//   phase 1  every segment but a sequence's last: E and A into a workspace, no outputs
+//   phase 2  every segment: its start state S <- diag(A_q) S + E_q over the segments q before it, begun
+//            from the sequence's state, then the recurrence with outputs; the last segment that holds
+//            tokens writes the state back
+// which changes the order of additions, nothing else.
+struct WkvSegments {
+    int segs;          // segments a sequence (1: none of this)
+    int seg_len;       // tokens a segment (a multiple of 8)
+    int phase;         // 0: the whole sequence in one go; 1, 2: see above
+    float* ends;       // [sequence][segment][head][d][d]
+    float* decays;     // [sequence][segment][head][d]
+};
+
 // A thread owns CPT = 4 neighbouring value columns and the rows i = kp + 8 m of them; a warp covers 16
 // columns, a block of four warps 64.  VEC: the state's rows are read and written 16 bytes at a time.
 template <int RPT, bool VEC>
@@ -150,13 +167,18 @@ __global__ void __launch_bounds__(SCAN_THREADS)
 wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
                 const float* __restrict__ w, long long ld, const float* __restrict__ u, float* __restrict__ state,
                 long long state_pitch, const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int heads,
-                int d, float* __restrict__ out) {
+                int d, float* __restrict__ out, const WkvSegments sg) {
     constexpr int SCAN_TOK = scan_tok(RPT);
     extern __shared__ __align__(16) float scan_smem[];     // [SCAN_TOK][3 d + SCAN_BCOLS]: r, k, decay, v of the block's columns
     pdl_sync();
-    const int seq = blockIdx.z, head = blockIdx.y;
-    const int tok0 = cu_seqlens[seq], cnt = cu_seqlens[seq + 1] - tok0;
+    const int seq = blockIdx.z / sg.segs, seg = blockIdx.z % sg.segs, head = blockIdx.y;
+    const int seq_tok0 = cu_seqlens[seq], seq_cnt = cu_seqlens[seq + 1] - seq_tok0;
+    // this block's tokens: the sequence's, or one segment of them
+    const int tok0 = seq_tok0 + seg * sg.seg_len;
+    const int cnt = sg.segs > 1 ? min(sg.seg_len, seq_cnt - seg * sg.seg_len) : seq_cnt;
     if (cnt <= 0) return;
+    const bool last_seg = sg.segs == 1 || (seg + 1) * sg.seg_len >= seq_cnt;       // the last one that holds tokens
+    if (sg.phase == 1 && last_seg) return;                                         // nothing comes after it
     const int kp = threadIdx.x % SCAN_KP, cg = threadIdx.x / SCAN_KP;      // row group, column group
     const int c0 = blockIdx.x * SCAN_BCOLS;                                // the block's first column
     const int col = c0 + cg * SCAN_CPT;                                    // this thread's first column
@@ -164,11 +186,17 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const 
     const int rowlen = 3 * d + SCAN_BCOLS;
     float* S = state + (size_t)slots[seq] * state_pitch + hc * d;          // [d (i)][d (j)] of this head
     float sreg[RPT][SCAN_CPT], ureg[RPT];
+    const size_t plane = (size_t)d * d;
+    float* ends = sg.ends ? sg.ends + ((size_t)seq * sg.segs * heads + head) * plane : nullptr;      // + segment * heads * plane
+    float* decays = sg.decays ? sg.decays + ((size_t)seq * sg.segs * heads + head) * d : nullptr;     // + segment * heads * d
 #pragma unroll
     for (int m = 0; m < RPT; m++) {
         const int i = kp * RPT + m;
         ureg[m] = i < d ? u[hc + i] : 0.f;
-        if (VEC && i < d && col < d) {
+        if (sg.phase == 1) {
+#pragma unroll
+            for (int c = 0; c < SCAN_CPT; c++) sreg[m][c] = 0.f;
+        } else if (VEC && i < d && col < d) {
             const float4 t4 = *reinterpret_cast<const float4*>(S + (size_t)i * d + col);
             sreg[m][0] = t4.x, sreg[m][1] = t4.y, sreg[m][2] = t4.z, sreg[m][3] = t4.w;
         } else {
@@ -176,6 +204,23 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const 
             for (int c = 0; c < SCAN_CPT; c++) sreg[m][c] = (i < d && col + c < d) ? S[(size_t)i * d + col + c] : 0.f;
         }
     }
+    if (sg.phase == 2)       // the segments before this one, in order: S <- diag(A_q) S + E_q
+        for (int q = 0; q < seg; q++) {
+            const float* aq = decays + (size_t)q * heads * d;
+            const float* eq = ends + (size_t)q * heads * plane;
+#pragma unroll
+            for (int m = 0; m < RPT; m++) {
+                const int i = kp * RPT + m;
+                if (i >= d) continue;
+                const float ai = aq[i];
+#pragma unroll
+                for (int c = 0; c < SCAN_CPT; c++)
+                    if (col + c < d) sreg[m][c] = fmaf(ai, sreg[m][c], eq[(size_t)i * d + col + c]);
+            }
+        }
+    float wprod[RPT];        // phase 1: the product of this thread's rows' decays
+#pragma unroll
+    for (int m = 0; m < RPT; m++) wprod[m] = 1.f;
     // what a thread brings into shared memory for a run of SCAN_TOK tokens: of every token the elements
     // x = thread, thread + 128, ... of [r | k | decay | the block's columns of v] (no division anywhere),
     // asked for one run ahead, so that their latency passes while the run before is worked on
@@ -217,6 +262,17 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const 
             const float* row = scan_smem + (size_t)tt * rowlen;
             const float4 v4 = *reinterpret_cast<const float4*>(row + 3 * d + cg * SCAN_CPT);
             const float vj[SCAN_CPT] = {v4.x, v4.y, v4.z, v4.w};
+            if (sg.phase == 1) {         // the end state and the decays' products alone
+#pragma unroll
+                for (int m = 0; m < RPT; m++) {
+                    const int i = kp * RPT + m;
+                    const float ki = i < d ? row[d + i] : 0.f, wi = i < d ? row[2 * d + i] : 0.f;
+                    wprod[m] *= wi;
+#pragma unroll
+                    for (int c = 0; c < SCAN_CPT; c++) sreg[m][c] = fmaf(wi, sreg[m][c], ki * vj[c]);
+                }
+                continue;
+            }
             float acc[SCAN_CPT] = {0.f, 0.f, 0.f, 0.f};
             // o[j] = sum_i r_i S[i][j] + v_j sum_i r_i u_i k_i: the bonus's sum is the same for every column
             float ruk = 0.f;
@@ -267,6 +323,15 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ k, const 
                 for (int c = 0; c < SCAN_CPT; c++)
                     if (col + c < d) o[c] = acc[c];
             }
+        }
+    }
+    if (sg.phase == 2 && !last_seg) return;          // only the sequence's last segment leaves the state behind
+    if (sg.phase == 1) {
+        S = ends + (size_t)seg * heads * plane;
+        if (cg == 0 && blockIdx.x == 0) {
+#pragma unroll
+            for (int m = 0; m < RPT; m++)
+                if (kp * RPT + m < d) decays[(size_t)seg * heads * d + kp * RPT + m] = wprod[m];
         }
     }
 #pragma unroll
@@ -354,28 +419,35 @@ MOE_API int moe_wkv_decay(const float* low, const float* w2t, const float* w0, i
 // out: [T, heads * d] 32-bit (rows of no sequence are left alone).
 MOE_API int moe_wkv_scan(const float* r, const float* k, const float* v, const float* w, long long ld,
                          const float* u, float* state, long long state_pitch, const int* cu_seqlens, const int* slots,
-                         int num_seqs, int heads, int d, float* out, cudaStream_t stream) {
+                         int num_seqs, int heads, int d, float* out, int segs, int seg_len, float* ends, float* decays,
+                         cudaStream_t stream) {
     if (num_seqs <= 0) return 0;
     if (!r || !k || !v || !w || !u || !state || !out || heads <= 0 || d <= 0 || d > 256 ||
         ld < (long long)heads * d || state_pitch < (long long)heads * d * d || heads > 65535 || num_seqs > 65535)
         return (int)cudaErrorInvalidValue;
-    const dim3 grid((d + SCAN_BCOLS - 1) / SCAN_BCOLS, heads, num_seqs);
+    if (segs < 1 || (segs > 1 && (!ends || !decays || seg_len <= 0 || seg_len % 8 || (long long)num_seqs * segs > 65535)))
+        return (int)cudaErrorInvalidValue;
+    const dim3 grid((d + SCAN_BCOLS - 1) / SCAN_BCOLS, heads, num_seqs * segs);
     const size_t smem = (size_t)scan_tok(d > 128 ? 32 : 8) * (3 * d + SCAN_BCOLS) * sizeof(float);
     // rows of the state 16 bytes at a time where every row of every head starts on such a boundary
-    const bool vec = d % 4 == 0 && state_pitch % 4 == 0 && ((uintptr_t)state % 16) == 0;
-#define SCAN(RPT_)                                                                                                \
-    do {                                                                                                          \
-        if (vec)                                                                                                  \
-            return launch_pdl(wkv_scan_kernel<RPT_, true>, grid, SCAN_THREADS, smem, stream, r, k, v, w, ld, u,     \
-                              state, state_pitch, cu_seqlens, slots, heads, d, out);                              \
-        return launch_pdl(wkv_scan_kernel<RPT_, false>, grid, SCAN_THREADS, smem, stream, r, k, v, w, ld, u, state, \
-                          state_pitch, cu_seqlens, slots, heads, d, out);                                         \
-    } while (0)
-    if (d <= 32) SCAN(4);
-    if (d <= 64) SCAN(8);
-    if (d <= 128) SCAN(16);
-    SCAN(32);
+    const bool vec = d % 4 == 0 && state_pitch % 4 == 0 && ((uintptr_t)state % 16) == 0 && ((uintptr_t)ends % 16) == 0;
+    // one launch, or phase 1 and then phase 2 of the segmented form
+    for (int phase = segs > 1 ? 1 : 0; phase <= (segs > 1 ? 2 : 0); phase++) {
+        const WkvSegments sg{segs, seg_len, phase, ends, decays};
+        int code;
+#define SCAN(RPT_)                                                                                                    \
+    code = vec ? launch_pdl(wkv_scan_kernel<RPT_, true>, grid, SCAN_THREADS, smem, stream, r, k, v, w, ld, u, state,       \
+                            state_pitch, cu_seqlens, slots, heads, d, out, sg)                                        \
+               : launch_pdl(wkv_scan_kernel<RPT_, false>, grid, SCAN_THREADS, smem, stream, r, k, v, w, ld, u, state,      \
+                            state_pitch, cu_seqlens, slots, heads, d, out, sg)
+        if (d <= 32) SCAN(4);
+        else if (d <= 64) SCAN(8);
+        else if (d <= 128) SCAN(16);
+        else SCAN(32);
 #undef SCAN
+        if (code) return code;
+    }
+    return 0;
 }
 
 // o: [T, heads * d] 32-bit; gate: the gate projection's output, 32-bit, row pitch ldg; norm_w: [heads * d];

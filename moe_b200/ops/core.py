@@ -62,7 +62,7 @@ def lib():
             "moe_conv_state_update": [P, I, P, LL, I, I, P, P, I, P],
             "moe_wkv_shift_mix": [P, P, I, P, LL, P, P, P, P, I, I, P, I, P, P, P, P, I, I, P, P],
             "moe_wkv_decay": [P, P, P, I, I, I, P, P],
-            "moe_wkv_scan": [P, P, P, P, LL, P, P, LL, P, P, I, I, I, P, P],
+            "moe_wkv_scan": [P, P, P, P, LL, P, P, LL, P, P, I, I, I, P, I, I, P, P, P],
             "moe_wkv_finish": [P, P, LL, P, F, P, I, I, I, P, I, P],
             "moe_rmsnorm_scaled": [P, P, P, P, P, P, P, P, P, I, I, I, F, I, P, P, P, P, I, P, P, P, P],
             "moe_attention_decode_fused": [P, P, I, P, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, I, P, P],
@@ -82,7 +82,7 @@ def lib():
             "moe_pair_norm_mean": [P, P, P, P, F, I, I, P, P],
             "moe_relu2": [P, P, I, LL, P],
             "moe_table_route": [P, I, P, P, P, P, I, I, I, I, P, P, P, P],
-            "moe_ssd_scan": [P, LL, P, LL, P, P, P, P, LL, P, P, I, I, I, I, I, P, P],
+            "moe_ssd_scan": [P, LL, P, LL, P, P, P, P, LL, P, P, I, I, I, I, I, P, I, I, P, P, P],
             "moe_ssd_finish": [P, P, LL, P, F, P, I, I, I, P, I, P],
         }
         for name, argtypes in sig.items():
@@ -536,11 +536,12 @@ def wkv_decay(low, w2t, w0, out):
     _ok(lib().moe_wkv_decay(_p(low), _p(w2t), _p(w0), T, inner, R, _p(out), _stream()), "wkv_decay")
 
 
-def wkv_scan(r, k, v, w, u, state, batch, out, *, heads, d):
+def wkv_scan(r, k, v, w, u, state, batch, out, *, heads, d, segments=None):
     """Per sequence and head, tokens in order: o_t = (S + diag(u) k_t v_t^T)^T r_t, then
     S <- diag(w_t) S + k_t v_t^T.  r, k, v, w: float32 [T, heads * d] of one row pitch
     (column slices of one buffer are fine); ``state``: float32 [slots + 1, >= heads * d * d], S of every
-    slot; out: float32 [T, heads * d]."""
+    slot; out: float32 [T, heads * d].  ``segments``: into how many pieces that run side by side every
+    sequence's tokens are cut (None: ``scan_segments`` decides)."""
     T = out.shape[0]
     for t in (r, k, v, w):
         if (not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or tuple(t.shape) != (T, heads * d)
@@ -549,8 +550,16 @@ def wkv_scan(r, k, v, w, u, state, batch, out, *, heads, d):
     _chk(u, "u", torch.float32), _chk(out, "out", torch.float32, 2)
     if u.numel() != heads * d or state.dtype != torch.float32 or state.stride(1) != 1:
         raise KernelError("wkv_scan: constants or state")
+    segs = scan_segments(batch, heads * -(-d // 64), out.device) if segments is None else int(segments)
+    seg_len, ends, decays = 0, None, None
+    if segs > 1:
+        longest = int(getattr(batch, "max_new", 0) or 0) or T
+        seg_len = -(-(-(-longest // segs)) // 16) * 16
+        ends = torch.empty((batch.num_seqs, segs, heads, d, d), dtype=torch.float32, device=out.device)
+        decays = torch.empty((batch.num_seqs, segs, heads, d), dtype=torch.float32, device=out.device)
     _ok(lib().moe_wkv_scan(_p(r), _p(k), _p(v), _p(w), r.stride(0), _p(u), _p(state), state.stride(0),
-                           _p(batch.cu_seqlens), _p(batch.slots), batch.num_seqs, heads, d, _p(out), _stream()), "wkv_scan")
+                           _p(batch.cu_seqlens), _p(batch.slots), batch.num_seqs, heads, d, _p(out), segs, seg_len, _p(ends),
+                           _p(decays), _stream()), "wkv_scan")
 
 
 def wkv_finish(o, gate, norm_w, eps, batch, out, *, heads, d):
@@ -1254,11 +1263,29 @@ def table_route(table, batch, top_k, num_experts, topk_idx, topk_w, status):
                               _p(topk_idx), _p(topk_w), _p(status), _stream()), "table_route")
 
 
-def ssd_scan(xbc, dt_raw, dt_bias, a_log, dskip, state, batch, y, *, heads, groups, n, dv, offset=0):
+def scan_segments(batch, blocks_per_sequence: int, device) -> int:
+    """Into how many segments a sequence's tokens are cut for ``ssd_scan`` and ``wkv_scan``: one where the launch fills
+    the GPU anyway or the sequences are short; else enough to fill it, of at least 128 tokens each, eight
+    at most.  (``MOE_B200_SCAN_SEGMENTS``: 0 this rule, n > 0 that many.)"""
+    forced = int(os.environ.get("MOE_B200_SCAN_SEGMENTS", "0"))
+    longest = int(getattr(batch, "max_new", 0) or 0)
+    if forced > 0:
+        return max(1, min(forced, 64))
+    if longest < 256:
+        return 1
+    idx = torch.device(device).index or 0
+    if idx not in _SMS:
+        _SMS[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    room = (2 * _SMS[idx]) // max(1, batch.num_seqs * blocks_per_sequence)
+    return max(1, min(8, room, longest // 128))
+
+
+def ssd_scan(xbc, dt_raw, dt_bias, a_log, dskip, state, batch, y, *, heads, groups, n, dv, offset=0, segments=None):
     """Per sequence and head, tokens in order: dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S +
     dt B x^T, y = S^T C + dskip x.  ``xbc``: float32 [T, heads * dv + 2 groups n] = [x | B | C]; ``dt_raw``:
     float32 [T, heads] (a column slice is fine); ``state``: float32 [slots + 1, ...] whose rows hold
-    heads * n * dv floats from ``offset``; y: float32 [T, heads * dv]."""
+    heads * n * dv floats from ``offset``; y: float32 [T, heads * dv].  ``segments``: into how many pieces
+    that run side by side every sequence's tokens are cut (None: ``scan_segments`` decides)."""
     _chk(xbc, "xbc", torch.float32, 2), _chk(y, "y", torch.float32, 2)
     for t in (dt_bias, a_log, dskip):
         _chk(t, "per-head constant", torch.float32, 1)
@@ -1267,9 +1294,17 @@ def ssd_scan(xbc, dt_raw, dt_bias, a_log, dskip, state, batch, y, *, heads, grou
             or xbc.shape != (T, heads * dv + 2 * groups * n) or y.shape[1] != heads * dv or state.dtype != torch.float32
             or state.stride(1) != 1 or offset + heads * n * dv > state.shape[1] or dt_bias.numel() != heads):
         raise KernelError("ssd_scan: shapes")
+    segs = scan_segments(batch, heads * -(-dv // 64), y.device) if segments is None else int(segments)
+    seg_len, ends, decays = 0, None, None
+    if segs > 1:
+        longest = int(getattr(batch, "max_new", 0) or 0) or T
+        seg_len = -(-(-(-longest // segs)) // 16) * 16
+        ends = torch.empty((batch.num_seqs, segs, heads, n, dv), dtype=torch.float32, device=y.device)
+        decays = torch.empty((batch.num_seqs, segs, heads), dtype=torch.float32, device=y.device)
     _ok(lib().moe_ssd_scan(_p(xbc), xbc.stride(0), _p(dt_raw), dt_raw.stride(0), _p(dt_bias), _p(a_log), _p(dskip),
                            state.data_ptr() + 4 * offset, state.stride(0), _p(batch.cu_seqlens), _p(batch.slots),
-                           batch.num_seqs, heads, groups, n, dv, _p(y), _stream()), "ssd_scan")
+                           batch.num_seqs, heads, groups, n, dv, _p(y), segs, seg_len, _p(ends), _p(decays), _stream()),
+        "ssd_scan")
 
 
 def ssd_finish(y, z, norm_w, eps, batch, out, *, norm_groups):

@@ -422,6 +422,89 @@ def test_state_space_recurrence_and_gated_norm_over_steps(heads, groups, n, dv, 
         assert err < (1e-2 if bf16 else 2e-5), (s, err)
 
 
+@pytest.mark.parametrize("heads,groups,n,dv,segments", [(2, 1, 24, 16, 4), (3, 3, 64, 40, 3), (1, 1, 130, 64, 8), (2, 2, 16, 8, 2)])
+def test_state_space_recurrence_in_segments_side_by_side(heads, groups, n, dv, segments):
+    """Long sequences cut into segments that run side by side give what the chain over all tokens gives:
+    two sequences of unequal lengths (one shorter than a segment) that go on from a state left by an
+    earlier step, and the state they leave behind."""
+    from moe_b200.ops import core
+
+    g = torch.Generator().manual_seed(heads * 7 + n)
+    inner, ch = heads * dv, heads * dv + 2 * groups * n
+    lens = {0: 50 + 650, 1: 20 + 90}
+    rows = {s: torch.cat([torch.randn(m, ch, generator=g), torch.randn(m, heads, generator=g) - 1.0], 1) for s, m in lens.items()}
+    dt_bias, a_log, dsk = torch.randn(heads, generator=g), 0.5 * torch.randn(heads, generator=g) - 1.0, torch.randn(heads, generator=g)
+    got, states = {}, {}
+    for name, segs in (("chain", 1), ("segments", segments)):
+        state = torch.zeros((3, heads * n * dv), device="cuda")
+        outs = {0: [], 1: []}
+        for a0, a1, b0, b1, sg in ((0, 50, 0, 20, 1), (50, 700, 20, 110, segs)):
+            batch = G.make_batch("cuda", [1, 2], [a0, b0], [a1 - a0, b1 - b0])
+            r = dev(torch.cat([rows[0][a0:a1], rows[1][b0:b1]]))
+            y = torch.zeros((r.shape[0], inner), device="cuda")
+            core.ssd_scan(r[:, :ch].contiguous(), r[:, ch:], dev(dt_bias), dev(a_log), dev(dsk), state, batch, y, heads=heads,
+                          groups=groups, n=n, dv=dv, segments=sg)
+            outs[0].append(y[:a1 - a0].double().cpu()), outs[1].append(y[a1 - a0:].double().cpu())
+        got[name] = {s: torch.cat(v) for s, v in outs.items()}
+        states[name] = state.double().cpu()
+    grp = torch.arange(heads) // (heads // groups)
+    for s, m in lens.items():
+        r = rows[s].double()
+        xs, B = r[:, :inner].reshape(m, heads, dv), r[:, inner:inner + groups * n].reshape(m, groups, n)
+        C = r[:, inner + groups * n:ch].reshape(m, groups, n)
+        dt = plain.softplus(r[:, ch:] + dt_bias.double())
+        S = torch.zeros(heads, n, dv, dtype=F)
+        ref = torch.zeros(m, heads, dv, dtype=F)
+        for t in range(m):
+            S = torch.exp(-torch.exp(a_log.double()) * dt[t])[:, None, None] * S + dt[t][:, None, None] * B[t][grp][:, :, None] * xs[t][:, None, :]
+            ref[t] = torch.einsum("hn,hnv->hv", C[t][grp], S) + dsk.double()[:, None] * xs[t]
+        scale = float(ref.abs().max())
+        for name in got:
+            assert float((got[name][s] - ref.reshape(m, inner)).abs().max()) / scale < 2e-5, (name, s)
+            assert float((states[name][s + 1].reshape(heads, n, dv) - S).abs().max()) / float(S.abs().max()) < 2e-5, (name, s)
+
+
+@pytest.mark.parametrize("heads,d,segments", [(2, 32, 4), (3, 64, 3), (1, 80, 8), (2, 16, 2)])
+def test_recurrent_scan_in_segments_side_by_side(heads, d, segments):
+    """The recurrent mixer's scan cut into segments against the chain over all tokens and against the
+    recurrence written out: two sequences of unequal lengths that go on from a state left by an earlier
+    step, and the state they leave behind."""
+    from moe_b200.ops import core
+
+    g = torch.Generator().manual_seed(heads * 5 + d)
+    I = heads * d
+    lens = {0: 40 + 660, 1: 30 + 75}
+    r = {s: torch.randn(m, I, generator=g) / 4 for s, m in lens.items()}
+    k = {s: torch.randn(m, I, generator=g) / 4 for s, m in lens.items()}
+    v = {s: torch.randn(m, I, generator=g) for s, m in lens.items()}
+    w = {s: torch.exp(-torch.exp(torch.randn(m, I, generator=g) - 2.0)) for s, m in lens.items()}
+    u = torch.randn(heads, d, generator=g)
+    got, states = {}, {}
+    for name, segs in (("chain", 1), ("segments", segments)):
+        state = torch.zeros((3, 5 + I * d), device="cuda")
+        outs = {0: [], 1: []}
+        for a0, a1, b0, b1, sg in ((0, 40, 0, 30, 1), (40, 700, 30, 105, segs)):
+            batch = G.make_batch("cuda", [1, 2], [a0, b0], [a1 - a0, b1 - b0])
+            cat = lambda t: dev(torch.cat([t[0][a0:a1], t[1][b0:b1]]))
+            o = torch.zeros((a1 - a0 + b1 - b0, I), device="cuda")
+            core.wkv_scan(cat(r), cat(k), cat(v), cat(w), dev(u), state[:, 5:], batch, o, heads=heads, d=d, segments=sg)
+            outs[0].append(o[:a1 - a0].double().cpu()), outs[1].append(o[a1 - a0:].double().cpu())
+        got[name] = {s: torch.cat(x) for s, x in outs.items()}
+        states[name] = state[:, 5:].double().cpu()
+    for s, m in lens.items():
+        rr, kk, vv, ww = (t[s].double().reshape(m, heads, d) for t in (r, k, v, w))
+        S = torch.zeros(heads, d, d, dtype=F)
+        ref = torch.zeros(m, heads, d, dtype=F)
+        for t in range(m):
+            kv = kk[t][:, :, None] * vv[t][:, None, :]
+            ref[t] = torch.einsum("hi,hij->hj", rr[t], S + u.double()[:, :, None] * kv)
+            S = ww[t][:, :, None] * S + kv
+        scale = float(ref.abs().max())
+        for name in got:
+            assert float((got[name][s] - ref.reshape(m, I)).abs().max()) / scale < 2e-5, (name, s)
+            assert float((states[name][s + 1].reshape(heads, d, d) - S).abs().max()) / float(S.abs().max()) < 2e-5, (name, s)
+
+
 def test_half_the_sum_of_two_normed_rows_squared_relu_and_the_table():
     from moe_b200.ops import core
 
